@@ -1,1 +1,1 @@
-from . import llama  # noqa: F401 (registers LlamaForCausalLM)
+from . import llama, rugedra  # noqa: F401 (register LlamaForCausalLM and Rugedra)

@@ -29,9 +29,16 @@ class PagedGroupSpec:
     num_kv_heads: int
     head_dim: int
     window: int | None = None  # None: every position stays; else the latest ``window`` do
+    value_dim: int | None = None  # size of a value row: None = head_dim; 0 = no value rows are kept
+
+    @property
+    def values_per_token(self) -> int:
+        """Cached numbers one token adds in one layer of the group."""
+        v = self.head_dim if self.value_dim is None else self.value_dim
+        return self.num_kv_heads * (self.head_dim + v)
 
     def bytes_per_page(self, page_size: int, dtype_bytes: int) -> int:
-        return 2 * self.num_layers * self.num_kv_heads * self.head_dim * page_size * dtype_bytes
+        return self.num_layers * self.values_per_token * page_size * dtype_bytes
 
 
 @dataclass(frozen=True)

@@ -61,10 +61,14 @@ class CacheStorage:
         for spec, pool in zip(manager.paged_groups, manager.pools):
             shape = (spec.num_layers, pool.num_pages + 1, spec.num_kv_heads,
                      manager.page_size, spec.head_dim)
-            self.paged.append(PagedStorage(
-                torch.zeros(shape, dtype=dtype, device=device),
-                torch.zeros(shape, dtype=dtype, device=device),
-                manager.page_size, pool.num_pages, spec.window))
+            k = torch.zeros(shape, dtype=dtype, device=device)
+            if spec.value_dim is None:
+                v = torch.zeros(shape, dtype=dtype, device=device)
+            elif spec.value_dim == 0:  # the values are read out of the key rows
+                v = k
+            else:
+                v = torch.zeros((*shape[:-1], spec.value_dim), dtype=dtype, device=device)
+            self.paged.append(PagedStorage(k, v, manager.page_size, pool.num_pages, spec.window))
         self.state = [
             torch.zeros((spec.num_layers, manager.max_requests + 1, *spec.shape),
                         dtype=torch.float32, device=device)
@@ -72,5 +76,6 @@ class CacheStorage:
         ]
 
     def bytes(self) -> int:
-        total = sum(p.k.numel() * p.k.element_size() * 2 for p in self.paged)
+        total = sum(p.k.numel() * p.k.element_size() + (0 if p.v is p.k else p.v.numel() * p.v.element_size())
+                    for p in self.paged)
         return total + sum(s.numel() * 4 for s in self.state)

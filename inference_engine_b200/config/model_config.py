@@ -35,9 +35,11 @@ def id_tuple(value: Any) -> tuple[int, ...]:
 
 
 def architecture_name(raw: dict[str, Any]) -> str:
-    """``architectures[0]``, else ``model_type`` (engine/config.py:70-71)."""
+    """``architectures[0]``, else ``architecture``, else ``model_type`` (engine/config.py:70-71)."""
     archs = raw.get("architectures") or []
-    return str(archs[0]) if archs else str(raw.get("model_type", "unknown"))
+    if archs:
+        return str(archs[0])
+    return str(raw.get("architecture") or raw.get("model_type", "unknown"))
 
 
 def read_config_dict(model_dir: str | Path) -> dict[str, Any]:

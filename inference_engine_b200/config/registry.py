@@ -68,7 +68,12 @@ def config_from_dict(raw: dict[str, Any]) -> Any:
 
 
 def load_config(model_dir: str | Path) -> Any:
-    return config_from_dict(read_config_dict(model_dir))
+    """The typed configuration of a model folder.  A configuration class whose ``config.json``
+    leaves sizes to the tensors' shapes completes itself from the folder
+    (``complete_from_folder(model_dir) -> config``)."""
+    cfg = config_from_dict(read_config_dict(model_dir))
+    complete = getattr(cfg, "complete_from_folder", None)
+    return complete(model_dir) if complete is not None else cfg
 
 
 def build_model_spec(config: Any) -> ModelSpec:

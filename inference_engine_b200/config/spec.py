@@ -33,7 +33,7 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None  # None: the layer has a mixer only
     norms: dict[str, PartSpec]
 
 

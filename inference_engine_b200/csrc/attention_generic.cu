@@ -11,13 +11,22 @@
 // tensor-core kernels do not take.  Counterparts in the reference:
 // engine/kernels/paged_attention.py:44-87 (decode rows) and the gather + SDPA path
 // engine/model/layers.py:215-225 (prompt portions).
+// A value row may be shorter than a key row and may live inside it: `hdv` entries at the start of
+// rows `v_stride` apart (a mixer that caches one shared latent row per token passes the key cache
+// as the value cache too, `v_stride` = the key row and `hdv` = the latent's size).
 #include "common.cuh"
 #include <math.h>
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAX_ACC = 8;  // head_dim <= 256
+constexpr int MAX_ACC = 16;  // value rows of up to 512 entries
 
+template <typename T>
+__device__ __forceinline__ float dot_row_any(const float* __restrict__ q, const T* __restrict__ k, int hd) {
+    float s = 0.f;  // (rows that are not a multiple of 16 bytes: one entry at a time)
+    for (int d = 0; d < hd; ++d) s = fmaf(q[d], ie_load(k + d), s);
+    return s;
+}
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const float* __restrict__ k, int hd) {
     float s = 0.f;
     for (int d = 0; d < hd; d += 4) {
@@ -48,7 +57,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_cache, const int* __restrict__ block_tables,
                                int table_width, const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, T* __restrict__ out,
-                               int nh, int nkv, int hd, int page_size, int total_pages,
+                               int nh, int nkv, int hd, int hdv, int v_stride, int page_size, int total_pages,
                                float scale, int window, int* err) {
     extern __shared__ float q_smem[];  // [WARPS][hd]
     ie_pdl_trigger();
@@ -70,7 +79,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     float acc[MAX_ACC];
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) acc[i] = 0.f;
-    int nacc = (hd + 31) / 32;
+    int nacc = (hdv + 31) / 32;
 
     for (int t0 = (lo / 32) * 32; t0 <= pos; t0 += 32) {
         int kpos = t0 + lane;
@@ -84,7 +93,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                 valid = false;
             } else {
                 row = ((long long)page * nkv + kvh) * page_size + (kpos % page_size);
-                s = dot_row(qs, k_cache + row * hd, hd) * scale;
+                s = (hd % 8 == 0 ? dot_row(qs, k_cache + row * hd, hd) : dot_row_any(qs, k_cache + row * hd, hd)) * scale;
             }
         }
         float m_new = fmaxf(m, warp_max(s));
@@ -98,21 +107,21 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
             float pj = __shfl_sync(0xffffffffu, p, j);
             long long rj = __shfl_sync(0xffffffffu, row, j);
             if (rj < 0) continue;  // uniform across the warp
-            const T* vrow = v_cache + rj * hd;
+            const T* vrow = v_cache + rj * v_stride;
 #pragma unroll
             for (int i = 0; i < MAX_ACC; ++i) {
                 int d = lane + 32 * i;
-                if (i < nacc && d < hd) acc[i] = fmaf(pj, ie_load(vrow + d), acc[i]);
+                if (i < nacc && d < hdv) acc[i] = fmaf(pj, ie_load(vrow + d), acc[i]);
             }
         }
         m = m_new;
     }
-    T* orow = out + ((size_t)token * nh + head) * hd;
+    T* orow = out + ((size_t)token * nh + head) * hdv;
     float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) {
         int d = lane + 32 * i;
-        if (i < nacc && d < hd) ie_store(orow + d, acc[i] * inv);
+        if (i < nacc && d < hdv) ie_store(orow + d, acc[i] * inv);
     }
 }
 }  // namespace
@@ -120,11 +129,11 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
                                       int dtype, const int* block_tables, int table_width,
                                       const int* seq_of_token, const int* positions, void* out,
-                                      int num_tokens, int nh, int nkv, int hd, int page_size,
-                                      int total_pages, float scale, int window, int* err,
+                                      int num_tokens, int nh, int nkv, int hd, int hdv, int v_stride,
+                                      int page_size, int total_pages, float scale, int window, int* err,
                                       void* stream) {
     if (num_tokens <= 0) return 0;
-    if (hd % 8 != 0 || hd > 32 * MAX_ACC || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
+    if (hd < 1 || hdv < 1 || hdv > 32 * MAX_ACC || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     dim3 grid((nh + WARPS - 1) / WARPS, num_tokens);
     size_t smem = (size_t)WARPS * hd * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
@@ -132,11 +141,11 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             block_tables, table_width, seq_of_token, positions, (__nv_bfloat16*)out,
-            nh, nkv, hd, page_size, total_pages, scale, window, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, err);
     else
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_tables, table_width, seq_of_token, positions, (float*)out,
-            nh, nkv, hd, page_size, total_pages, scale, window, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, err);
     return IE_LAUNCH_CHECK();
 }

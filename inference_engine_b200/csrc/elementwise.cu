@@ -41,7 +41,7 @@ IE_API int ie_embedding(const void* table, int table_dtype, const int* ids, floa
 // ---------------------------------------------------------------------------------------------
 template <typename OutT, int THREADS>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
-                               size_t partial_stride, const float* __restrict__ weight, float eps,
+                               size_t partial_stride, float dscale, const float* __restrict__ weight, float eps,
                                OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     __shared__ float partial[THREADS / 32];
     __shared__ float inv_rms;
@@ -55,7 +55,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += THREADS) {
         float x = hrow[i];
-        if (drow) for (int p = 0; p < num_partials; ++p) x += drow[p * partial_stride + i];
+        if (drow) for (int p = 0; p < num_partials; ++p) x = fmaf(dscale, drow[p * partial_stride + i], x);
         if (write_back) hrow[i] = x;
         ss += x * x;
     }
@@ -73,7 +73,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
     OutT* orow = out + (size_t)r * hidden;
     for (int i = threadIdx.x; i < hidden; i += THREADS) {
         float x = hrow[i];
-        if (drow && !write_back) for (int p = 0; p < num_partials; ++p) x += drow[p * partial_stride + i];
+        if (drow && !write_back) for (int p = 0; p < num_partials; ++p) x = fmaf(dscale, drow[p * partial_stride + i], x);
         ie_store(orow + i, weight[i] * (x * scale));
     }
 }
@@ -94,7 +94,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 template <typename OutT, int THREADS, int VPT, int PCH>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
-                   size_t partial_stride, const float* __restrict__ weight, float eps,
+                   size_t partial_stride, float dscale, const float* __restrict__ weight, float eps,
                    OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     __shared__ float partial[THREADS / 32];
     __shared__ float inv_rms;
@@ -136,7 +136,8 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
                 if (p0 + j < num_partials) {
 #pragma unroll
                     for (int v = 0; v < VPT; ++v) {
-                        x[v].x += d[j][v].x; x[v].y += d[j][v].y; x[v].z += d[j][v].z; x[v].w += d[j][v].w;
+                        x[v].x = fmaf(dscale, d[j][v].x, x[v].x); x[v].y = fmaf(dscale, d[j][v].y, x[v].y);
+                        x[v].z = fmaf(dscale, d[j][v].z, x[v].z); x[v].w = fmaf(dscale, d[j][v].w, x[v].w);
                     }
                 }
         }
@@ -174,9 +175,9 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
 
 template <typename OutT>
 static int launch_rmsnorm(float* h, const float* delta, int num_partials, size_t partial_stride,
-                          const float* weight, float eps, OutT* out, const int* rows, int num_rows,
+                          float dscale, const float* weight, float eps, OutT* out, const int* rows, int num_rows,
                           int hidden, cudaStream_t s) {
-#define IE_NORM_ARGS s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden
+#define IE_NORM_ARGS s, h, delta, num_partials, partial_stride, dscale, weight, eps, out, rows, hidden
     bool multi = delta != nullptr && num_partials > 1;
     if (hidden % 4 == 0 && hidden <= 128 * 4 * 2)
         return multi ? ie_launch(rmsnorm_vec_kernel<OutT, 128, 2, 8>, dim3(num_rows), dim3(128), 0, IE_NORM_ARGS)
@@ -188,20 +189,181 @@ static int launch_rmsnorm(float* h, const float* delta, int num_partials, size_t
         return multi ? ie_launch(rmsnorm_vec_kernel<OutT, 512, 4, 4>, dim3(num_rows), dim3(512), 0, IE_NORM_ARGS)
                      : ie_launch(rmsnorm_vec_kernel<OutT, 512, 4, 1>, dim3(num_rows), dim3(512), 0, IE_NORM_ARGS);
 #undef IE_NORM_ARGS
-    return ie_launch(rmsnorm_kernel<OutT, 256>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    return ie_launch(rmsnorm_kernel<OutT, 256>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, dscale, weight, eps, out, rows, hidden);
 }
 
 // `delta` may be the sum of `num_partials` arrays `partial_stride` floats apart (the parts of
 // a matrix product that was split along its inner dimension); they are added in order.
+// What is added is `delta_scale * delta` (a model's residual multiplier; 1 adds delta as it is).
 IE_API int ie_rmsnorm(float* h, const float* delta, int num_partials, long long partial_stride,
-                      const float* weight, float eps, void* out, int out_dtype, const int* rows,
-                      int num_rows, int hidden, void* stream) {
+                      float delta_scale, const float* weight, float eps, void* out, int out_dtype,
+                      const int* rows, int num_rows, int hidden, void* stream) {
     if (num_rows <= 0) return 0;
     if (delta != nullptr && num_partials < 1) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == IE_BF16)
-        return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, weight, eps, (__nv_bfloat16*)out, rows, num_rows, hidden, s);
-    return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, weight, eps, (float*)out, rows, num_rows, hidden, s);
+        return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, delta_scale, weight, eps, (__nv_bfloat16*)out, rows, num_rows, hidden, s);
+    return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, delta_scale, weight, eps, (float*)out, rows, num_rows, hidden, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer norm (weight, no bias) with residual add:
+//   x = h[r] + delta_scale * sum_p delta_p[r];  out[r] = (x - mean(x)) / sqrt(mean((x - mean)^2) + eps) * w
+// Same conventions as the RMS norm above (rows == nullptr: h is updated in place; else the rows
+// are picked and h stays).  One block per row; the row lives in registers (up to 4 * THREADS * VPT
+// wide) or is read again from memory; mean and variance are taken in two passes, each summed in
+// an order that depends on the row's width alone.
+// ---------------------------------------------------------------------------------------------
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    __syncthreads();  // (scratch may still be read from the previous call)
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) total += scratch[w];
+    return total;
+}
+
+template <typename OutT, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+layernorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
+                 size_t partial_stride, float dscale, const float* __restrict__ weight, float eps,
+                 OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[THREADS / 32];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int r = blockIdx.x;
+    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    bool write_back = (rows == nullptr) && (delta != nullptr);
+    float sum = 0.f, sq = 0.f;
+    auto value = [&](int i) {  // the row's entry i with the deltas added (the row is not in registers)
+        float val = h[src + i];
+        if (delta && !write_back) for (int p = 0; p < num_partials; ++p) val = fmaf(dscale, delta[p * partial_stride + src + i], val);
+        return val;
+    };
+    if (hidden <= THREADS * VPT) {
+        float x[VPT];
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            int i = v * THREADS + threadIdx.x;
+            x[v] = 0.f;
+            if (i < hidden) {
+                float val = h[src + i];
+                if (delta) for (int p = 0; p < num_partials; ++p) val = fmaf(dscale, delta[p * partial_stride + src + i], val);
+                if (write_back) h[src + i] = val;
+                x[v] = val;
+                sum += val;
+            }
+        }
+        float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            float d = x[v] - mean;
+            if (v * THREADS + threadIdx.x < hidden) sq += d * d;
+        }
+        float inv = 1.0f / sqrtf(block_sum<THREADS>(sq, scratch) / (float)hidden + eps);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            int i = v * THREADS + threadIdx.x;
+            if (i < hidden) ie_store(out + (size_t)r * hidden + i, (x[v] - mean) * inv * weight[i]);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < hidden; i += THREADS) {
+        float val = h[src + i];
+        if (delta) for (int p = 0; p < num_partials; ++p) val = fmaf(dscale, delta[p * partial_stride + src + i], val);
+        if (write_back) h[src + i] = val;
+        sum += val;
+    }
+    float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;
+    for (int i = threadIdx.x; i < hidden; i += THREADS) {
+        float d = value(i) - mean;
+        sq += d * d;
+    }
+    float inv = 1.0f / sqrtf(block_sum<THREADS>(sq, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += THREADS)
+        ie_store(out + (size_t)r * hidden + i, (value(i) - mean) * inv * weight[i]);
+}
+
+IE_API int ie_layernorm(float* h, const float* delta, int num_partials, long long partial_stride,
+                        float delta_scale, const float* weight, float eps, void* out, int out_dtype,
+                        const int* rows, int num_rows, int hidden, void* stream) {
+    if (num_rows <= 0) return 0;
+    if (delta != nullptr && num_partials < 1) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16)
+        return ie_launch(layernorm_kernel<__nv_bfloat16, 256, 16>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials,
+                         (size_t)partial_stride, delta_scale, weight, eps, (__nv_bfloat16*)out, rows, hidden);
+    return ie_launch(layernorm_kernel<float, 256, 16>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials,
+                     (size_t)partial_stride, delta_scale, weight, eps, (float*)out, rows, hidden);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Learned positions: h[n, :] += float(table[positions[n], :]);  a position outside the table is
+// reported and skipped.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_position_rows_kernel(float* __restrict__ h, const T* __restrict__ table,
+                                         const int* __restrict__ positions, int hidden, int table_rows, int* err) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int row = blockIdx.x, pos = positions[row];
+    if (pos < 0 || pos >= table_rows) {
+        if (threadIdx.x == 0) ie_report(err, IE_ERR_POSITION, pos, row);
+        return;
+    }
+    const T* src = table + (size_t)pos * hidden;
+    float* dst = h + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] += ie_load(src + i);
+}
+
+IE_API int ie_add_position_rows(float* h, const void* table, int table_dtype, const int* positions,
+                                int num_tokens, int hidden, int table_rows, int* err, void* stream) {
+    if (num_tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == IE_BF16)
+        return ie_launch(add_position_rows_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, s, h,
+                         (const __nv_bfloat16*)table, positions, hidden, table_rows, err);
+    return ie_launch(add_position_rows_kernel<float>, dim3(num_tokens), dim3(128), 0, s, h, (const float*)table,
+                     positions, hidden, table_rows, err);
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = relu(x)^2 element by element (32-bit arithmetic, one rounding), and t *= factor in place.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ out, size_t count) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        float v = fmaxf(ie_load(x + i), 0.f);
+        ie_store(out + i, v * v);
+    }
+}
+
+IE_API int ie_relu_squared(const void* x, void* out, int dtype, long long count, void* stream) {
+    if (count <= 0) return 0;
+    int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IE_BF16)
+        return ie_launch(relu_squared_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)x,
+                         (__nv_bfloat16*)out, (size_t)count);
+    return ie_launch(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)x, (float*)out, (size_t)count);
+}
+
+__global__ void scale_kernel(float* __restrict__ t, float factor, size_t count) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        t[i] *= factor;
+}
+
+IE_API int ie_scale(float* t, float factor, long long count, void* stream) {
+    if (count <= 0) return 0;
+    int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    return ie_launch(scale_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, t, factor, (size_t)count);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -95,7 +95,7 @@ class Model:
                 table.append((req, 1))
                 gi = len(table) - 1
                 self.bindings.append(CacheBinding(gi if table is paged else -1 - gi, 0))
-        self.paged_groups = [PagedGroupSpec(n, r.num_kv_heads, r.head_dim, r.window) for r, n in paged]
+        self.paged_groups = [PagedGroupSpec(n, r.num_kv_heads, r.head_dim, r.window, r.value_dim) for r, n in paged]
         self.state_groups = [StateGroupSpec(n, tuple(r.shape)) for r, n in state]
         # Context groups are listed paged first, then state: remap the negative indices.
         n_paged = len(self.paged_groups)
@@ -110,7 +110,7 @@ class Model:
         from ..config.model_config import Footprint
 
         parameters = sum(math.prod(d.shape) for d in self.declared_weights().values())
-        per_token = sum(2 * g.num_layers * g.num_kv_heads * g.head_dim for g in self.paged_groups)
+        per_token = sum(g.num_layers * g.values_per_token for g in self.paged_groups)
         per_request = sum(g.num_layers * math.prod(g.shape) for g in self.state_groups)
         return Footprint(parameters, per_token, per_request)
 
@@ -122,13 +122,15 @@ class Model:
         h = self.embedding.forward(ctx.token_ids, ctx)
         for pos in self.positions.values():
             pos.apply_to_embedding(h, ctx)
-        delta = None
+        delta, scale = None, 1.0  # the pending delta and the factor it is to be added with
         for entry, binding in zip(self.spec.schedule, self.bindings):
-            delta = self.blocks[entry.layer].forward(h, delta, ctx, binding)
+            block = self.blocks[entry.layer]
+            delta = block.forward(h, delta, ctx, binding, delta_scale=scale)
+            scale = block.residual_mult
         if logit_rows is None or logit_rows.shape[0] == 0:
             # Nothing is read back, but the last add still belongs to the step.
             return None
-        x = self.final_norm.add_norm(h, delta, ctx, rows=logit_rows, tag="norm.final")
+        x = self.final_norm.add_norm(h, delta, ctx, rows=logit_rows, tag="norm.final", delta_scale=scale)
         return self.head.forward(x, ctx)
 
 

@@ -55,6 +55,9 @@ class ModelRunner:
             return (0,) * len(groups)
         answers = []
         for g in groups:
+            if getattr(g, "value_dim", None) is not None:  # (not the tensor-core decode kernels' kind of cache)
+                answers.append(0)
+                continue
             seen = ctx_lens if g.window is None else [min(c, g.window) for c in ctx_lens]
             answers.append(int(decide(seen, g.num_kv_heads, getattr(g, "head_dim", None))))
         return tuple(answers)

@@ -151,12 +151,28 @@ def build_attention(head_dim: int) -> Path:
                          [f"-DIE_HD={head_dim}"])
 
 
+# Kernels only some mixers and feed-forwards need, each a library of its own that is built the
+# first time a model with such a part runs: name -> source.
+PART_LIBRARIES = {
+    "latent": "latent_attention.cu",  # the latent attention's input stage and per-head products
+    "delta": "delta_rule.cu",  # the gated delta rule: convolutions, the recurrence, the read-out norm
+    "routed": "routed_experts.cu",  # routing and the grouped products of the routed feed-forward
+}
+
+
+def build_part_library(name: str) -> Path:
+    if name not in PART_LIBRARIES:
+        raise BuildError(f"no kernel library {name!r}; there are {sorted(PART_LIBRARIES)}")
+    return build_library(f"ie_b200_{name}", [PART_LIBRARIES[name]])
+
+
 def build_all(prune: bool = True) -> list[Path]:
     """Every library the package can load (the build check compiles them all).  With `prune`,
     libraries of this package in the build folder that belong to older sources are removed."""
     libs = [build_core(), build_selftest()]
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 2) as pool:
         libs += list(pool.map(build_attention, ATTENTION_HEAD_DIMS))
+        libs += list(pool.map(build_part_library, PART_LIBRARIES))
     if prune:
         keep = {lib.name for lib in libs}
         for old in build_dir().glob("libie_b200_*.so"):

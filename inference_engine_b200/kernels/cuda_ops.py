@@ -17,7 +17,7 @@ import functools
 import os
 from ctypes import c_float, c_int, c_void_p
 
-from .build import ATTENTION_HEAD_DIMS, build_attention, build_core
+from .build import ATTENTION_HEAD_DIMS, build_attention, build_core, build_part_library
 
 _ERRORS = {
     1: "a token id outside the vocabulary",
@@ -122,6 +122,7 @@ class CudaOps:
         self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
+        self._part_libs: dict[str, object] = {}
         self._argmax_scratch = None
         self._tickets = None
         self._retired_tickets = []
@@ -195,7 +196,11 @@ class CudaOps:
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
         sigs = {
             "ie_embedding": [P, I, P, P, I, I, I, P, P],
-            "ie_rmsnorm": [P, P, I, L, P, F, P, I, P, I, I, P],
+            "ie_rmsnorm": [P, P, I, L, F, P, F, P, I, P, I, I, P],
+            "ie_layernorm": [P, P, I, L, F, P, F, P, I, P, I, I, P],
+            "ie_add_position_rows": [P, P, I, P, I, I, I, P, P],
+            "ie_relu_squared": [P, P, I, L, P],
+            "ie_scale": [P, F, L, P],
             "ie_rope_kv_write": [P, I, L, P, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P, P],
             "ie_silu_mul": [P, I, I, L, P, I, I, I, I, P],
             "ie_gemm_tma_gated_bf16": [P, P, P, I, I, I, P, P],
@@ -204,7 +209,7 @@ class CudaOps:
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_ok": [I, I, I],
-            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
+            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
         }
         for name, args in sigs.items():
@@ -298,12 +303,40 @@ class CudaOps:
         return t.shape[0], t.stride(0)
 
     @_kind("norm")
-    def rmsnorm(self, h, delta, weight, eps, out, rows=None) -> None:
+    def rmsnorm(self, h, delta, weight, eps, out, rows=None, delta_scale: float = 1.0) -> None:
         n = h.shape[0] if rows is None else rows.shape[0]
         parts, stride = self._partials(delta)
-        self._check(self._rmsnorm(h.data_ptr(), self._ptr(delta), parts, stride, weight.data_ptr(), eps,
-                                  out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
+        self._check(self._rmsnorm(h.data_ptr(), self._ptr(delta), parts, stride, delta_scale, weight.data_ptr(),
+                                  eps, out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
                                   h.shape[1], self._stream()), "rmsnorm")
+
+    @_kind("norm")
+    def layernorm(self, h, delta, weight, eps, out, rows=None, delta_scale: float = 1.0) -> None:
+        """Layer norm (weight, no bias) of ``h + delta_scale * delta``; the conventions of :meth:`rmsnorm`."""
+        n = h.shape[0] if rows is None else rows.shape[0]
+        parts, stride = self._partials(delta)
+        self._check(self._layernorm(h.data_ptr(), self._ptr(delta), parts, stride, delta_scale, weight.data_ptr(),
+                                    eps, out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
+                                    h.shape[1], self._stream()), "layernorm")
+
+    @_kind("embedding")
+    def add_position_rows(self, h, table, positions) -> None:
+        """``h[n] += table[positions[n]]`` (a learned position vector per token)."""
+        self._check(self._add_position_rows(h.data_ptr(), table.data_ptr(), _dtype_code(table),
+                                            positions.data_ptr(), h.shape[0], h.shape[1], table.shape[0],
+                                            self._err_ptr, self._stream()), "add_position_rows")
+
+    @_kind("activation")
+    def relu_squared(self, x, out) -> None:
+        if x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous():
+            raise KernelError("relu_squared takes contiguous tensors of one dtype")
+        self._check(self._relu_squared(x.data_ptr(), out.data_ptr(), _dtype_code(x), x.numel(), self._stream()),
+                    "relu_squared")
+
+    @_kind("head")
+    def scale_(self, t, factor: float) -> None:
+        """``t *= factor`` for a contiguous 32-bit tensor."""
+        self._check(self._scale(t.data_ptr(), float(factor), t.numel(), self._stream()), "scale")
 
     FEW_ROWS = 16  # up to this many rows a bfloat16 product runs the weight-streaming kernel
 
@@ -669,16 +702,20 @@ class CudaOps:
         return best if cost(best) <= 0.75 * cost(1) else 1
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
-                        scale, window, out, ragged: bool | None = None) -> None:
+                        scale, window, out, ragged: bool | None = None, value_dim: int | None = None) -> None:
         """Attention of every token of the step over its request's cached keys and values.
         bfloat16 with a head size the tensor-core kernels take and at most 16 query heads per
         key/value head: requests with few rows go to the split decode kernel, longer portions
         to the prefill kernel.  Everything else (32-bit, other head sizes) runs the general
         kernel, whose order of operations does not depend on the batch."""
-        if hd % 8 or hd > 256:
-            raise KernelError(f"head_dim {hd} is not supported: it must be a multiple of 8, at most 256")
         if nkv < 1 or nh % nkv:
             raise KernelError(f"{nh} query heads cannot share {nkv} key/value heads")
+        if value_dim is not None and value_dim != hd:
+            # value rows shorter than key rows (a shared latent row whose first entries are the value)
+            return self.latent_paged_attention(q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, value_dim,
+                                               page_size, scale, window, out)
+        if hd % 8 or hd > 256:
+            raise KernelError(f"head_dim {hd} is not supported: it must be a multiple of 8, at most 256")
         groups = nh // nkv
         if q.dtype == self.torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
             lib = self._attention_lib(hd)
@@ -816,8 +853,174 @@ class CudaOps:
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
-            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, page_size,
+            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, hd, hd, page_size,
             k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
+
+    @_kind("attention.latent")
+    def latent_paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, value_dim,
+                               page_size, scale, window, out) -> None:
+        """Attention whose value rows are the first ``value_dim`` entries of ``v_cache``'s rows
+        (``v_cache`` may be the key cache itself); ``out`` is ``[N, nh * value_dim]``."""
+        if not 0 < value_dim <= 512:
+            raise KernelError(f"value rows of {value_dim} entries are not supported (1 to 512)")
+        self._check(self._paged_attention_generic(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
+            block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
+            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, value_dim,
+            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, self._err_ptr, self._stream()),
+            "paged_attention_latent")
+
+    # --- kernels of single mixers and feed-forwards (libraries built on first use) -------------
+
+    _PART_SIGNATURES = {
+        "latent": {
+            "ie_latent_prep": "P I P P I I P F P P P P I P I I I I I I P P",
+            "ie_headwise_linear": "P L L P P L L P I I I I I P",
+        },
+        "delta": {
+            "ie_delta_prep": "P I P P P P P L P P P P P P P P I I I I I I I I P P",
+            "ie_delta_rule": "P P P P P P L P P P I I I I I I P",
+            "ie_gated_rms_heads": "P P F P P I L I P",
+        },
+        "routed": {
+            "ie_route_topk": "P I P I I I I I I P P P",
+            "ie_routed_max_tiles": "I I",
+            "ie_routed_align": "P I I P P P I P",
+            "ie_routed_gate_up": "P P P I P P P I I I I F I F F P",
+            "ie_routed_down": "P P P P I P P P I I I I I P",
+        },
+    }
+
+    def _part_lib(self, name: str):
+        lib = self._part_libs.get(name)
+        if lib is None:
+            path = build_part_library(name)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as exc:
+                raise KernelError(f"the kernel library {path} could not be loaded: {exc}") from exc
+            kinds = {"P": c_void_p, "I": c_int, "F": c_float, "L": ctypes.c_longlong}
+            for fn_name, sig in self._PART_SIGNATURES[name].items():
+                fn = getattr(lib, fn_name)
+                fn.argtypes, fn.restype = [kinds[k] for k in sig.split()], c_int
+            self._part_libs[name] = lib
+        return lib
+
+    @_kind("latent.prep")
+    def latent_prep(self, proj, positions, table, rot_dims, norm_w, eps, q_plain, q_abs, gate, cache,
+                    slot_mapping, heads, dim, rot_dim, rank, page_size) -> None:
+        """The latent attention's input stage (see ``csrc/latent_attention.cu``).  ``proj``: the fused
+        projection's 32-bit output ``[N, heads * (dim + rot_dim) + rank + rot_dim + heads]``;
+        ``cache``: ``[pages, 1, page_size, rank + rot_dim]``."""
+        if table is not None and table.shape[2] * 2 != rot_dims:
+            raise KernelError("rotary table does not match the rotated dims")
+        if proj.dtype != self.torch.float32 or proj.dim() != 2 or not proj.is_contiguous():
+            raise KernelError("latent_prep reads a contiguous 32-bit projection")
+        if proj.shape[1] != heads * (dim + rot_dim) + rank + rot_dim + heads or cache.shape[-1] != rank + rot_dim:
+            raise KernelError("latent_prep: the projection or the cache rows do not fit the sizes")
+        total_slots = cache.shape[0] * page_size
+        self._check(self._part_lib("latent").ie_latent_prep(
+            proj.data_ptr(), proj.shape[1], positions.data_ptr(), self._ptr(table), rot_dims,
+            0 if table is None else table.shape[0], norm_w.data_ptr(), eps, q_plain.data_ptr(), q_abs.data_ptr(),
+            gate.data_ptr(), cache.data_ptr(), _dtype_code(q_abs), self._ptr(slot_mapping), proj.shape[0],
+            heads, dim, rot_dim, rank, total_slots, self._err_ptr, self._stream()), "latent_prep")
+
+    @_kind("latent.headwise")
+    def headwise_linear(self, x, w, out, row_scale=None) -> None:
+        """``out[n, h, :] = w[h] @ x[n, h, :]`` (times ``row_scale[n, h]``): ``x`` ``[N, H, K]`` and
+        ``out`` ``[N, H, O]`` may be views with any token and head strides (entries contiguous),
+        ``w`` is ``[H, O, K]`` contiguous; 32-bit sums."""
+        n, heads, k = x.shape
+        o = w.shape[1]
+        if (x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous() or w.shape != (heads, o, k)
+                or out.shape != (n, heads, o) or x.dtype != w.dtype or out.dtype != w.dtype):
+            raise KernelError("headwise_linear: shapes, strides or dtypes do not fit")
+        self._check(self._part_lib("latent").ie_headwise_linear(
+            x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1),
+            self._ptr(row_scale), _dtype_code(x), n, heads, o, k, self._stream()), "headwise_linear")
+
+    @_kind("delta.prep")
+    def delta_prep(self, qkvb, a, conv_w, A_log, dt_bias, state, slots, ctx, q_out, k_out, v_out, beta,
+                   decay, heads, kv_heads, dim, vdim, taps) -> None:
+        """Convolutions, unit norms, step sizes and decays of the gated delta rule, and the slots'
+        kept convolution inputs moved on (see ``csrc/delta_rule.cu``).  ``state``: ``[slots, floats]``."""
+        channels = 2 * kv_heads * dim + heads * vdim
+        if qkvb.shape[1] != channels + heads or conv_w.shape != (channels, taps):
+            raise KernelError("delta_prep: the projection or the convolution weights do not fit the sizes")
+        self._check(self._part_lib("delta").ie_delta_prep(
+            qkvb.data_ptr(), qkvb.shape[1], a.data_ptr(), conv_w.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(),
+            state.data_ptr(), state.stride(0), slots.data_ptr(), ctx.seq_of_token.data_ptr(), ctx.cu_q.data_ptr(),
+            q_out.data_ptr(), k_out.data_ptr(), v_out.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+            qkvb.shape[0], ctx.num_seqs, heads, kv_heads, dim, vdim, taps, state.shape[0], self._err_ptr,
+            self._stream()), "delta_prep")
+        self.launches += 1 if taps > 1 else 0
+
+    @_kind("delta.rule")
+    def delta_rule(self, q, k, v, beta, decay, state, slots, ctx, out, heads, kv_heads, dim, vdim) -> None:
+        """The recurrence itself: every request's tokens of this step in order, from and to its slot."""
+        if dim > 256:
+            raise KernelError(f"the delta rule kernel takes key sizes up to 256, not {dim}")
+        self._check(self._part_lib("delta").ie_delta_rule(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), state.data_ptr(),
+            state.stride(0), slots.data_ptr(), ctx.cu_q.data_ptr(), out.data_ptr(), ctx.num_seqs, heads,
+            kv_heads, dim, vdim, state.shape[0], self._stream()), "delta_rule")
+
+    @_kind("delta.out")
+    def gated_rms_heads(self, o, weight, eps, gate_pre, out, heads, vdim) -> None:
+        """``out = o / rms(o) * weight * sigmoid(gate_pre)`` per (token, head) over ``vdim``."""
+        self._check(self._part_lib("delta").ie_gated_rms_heads(
+            o.data_ptr(), weight.data_ptr(), eps, gate_pre.data_ptr(), out.data_ptr(), _dtype_code(out),
+            o.shape[0] * heads, vdim, self._stream()), "gated_rms_heads")
+
+    @_kind("routed.route")
+    def route_topk(self, x, w_router, groups, keep, ids, weights) -> None:
+        """Softmax scores, group limit and the ``top`` experts per token with their normalised weights."""
+        self._check(self._part_lib("routed").ie_route_topk(
+            x.data_ptr(), _dtype_code(x), w_router.data_ptr(), x.shape[0], x.shape[1], w_router.shape[0],
+            ids.shape[1], groups, keep, ids.data_ptr(), weights.data_ptr(), self._stream()), "route_topk")
+
+    def routed_experts(self, x, ids, weights, w_gate_up, w_down, *, limit, alpha, up_offset, ws, tag="moe"):
+        """The chosen experts' weighted outputs as ``[top, N, hidden]`` 32-bit slices (to be added in
+        order).  ``w_gate_up``: ``[experts, 2, ff, hidden]``, ``w_down``: ``[experts, hidden, ff]``."""
+        torch = self.torch
+        lib = self._part_lib("routed")
+        n, top = ids.shape
+        experts, _, ff, hidden = w_gate_up.shape
+        pairs = n * top
+        max_tiles = lib.ie_routed_max_tiles(pairs, experts)
+        rows = max_tiles * lib.ie_routed_tile_rows()
+        index = ws.buffer(tag + ".index", 1, rows + max_tiles + 4, torch.int32, rows_cap=None)[0]
+        sorted_pairs, tile_expert, meta = index[:rows], index[rows: rows + max_tiles], index[rows + max_tiles:]
+        y = ws.buffer(tag + ".act", pairs, ff, x.dtype)
+        out = ws.buffer(tag + ".delta", pairs, hidden, torch.float32).view(top, n, hidden)
+        self._routed_align(lib, ids, pairs, experts, sorted_pairs, tile_expert, meta, max_tiles)
+        self._routed_gate_up(lib, x, w_gate_up, y, sorted_pairs, tile_expert, meta, max_tiles, top, hidden, ff,
+                             limit, alpha, up_offset)
+        self._routed_down(lib, y, w_down, out, weights, sorted_pairs, tile_expert, meta, max_tiles, top, n, ff, hidden)
+        return out
+
+    @_kind("routed.align")
+    def _routed_align(self, lib, ids, pairs, experts, sorted_pairs, tile_expert, meta, max_tiles) -> None:
+        self._check(lib.ie_routed_align(ids.data_ptr(), pairs, experts, sorted_pairs.data_ptr(),
+                                        tile_expert.data_ptr(), meta.data_ptr(), max_tiles, self._stream()),
+                    "routed_align")
+
+    @_kind("routed.gate_up")
+    def _routed_gate_up(self, lib, x, w, y, sorted_pairs, tile_expert, meta, max_tiles, top, hidden, ff, limit,
+                        alpha, up_offset) -> None:
+        self._check(lib.ie_routed_gate_up(
+            x.data_ptr(), w.data_ptr(), y.data_ptr(), _dtype_code(x), sorted_pairs.data_ptr(),
+            tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, hidden, ff,
+            0.0 if limit is None else float(limit), 0 if limit is None else 1, alpha, up_offset,
+            self._stream()), "routed_gate_up")
+
+    @_kind("routed.down")
+    def _routed_down(self, lib, y, w, out, weights, sorted_pairs, tile_expert, meta, max_tiles, top, n, ff,
+                     hidden) -> None:
+        self._check(lib.ie_routed_down(
+            y.data_ptr(), w.data_ptr(), out.data_ptr(), weights.data_ptr(), _dtype_code(y),
+            sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, n, ff, hidden,
+            self._stream()), "routed_down")
 
     @_kind("activation")
     def silu_mul(self, gate_up, out, interleave: int = 0) -> None:

@@ -1,4 +1,6 @@
-from . import attention, block, embedding, feedforward, norm, position  # noqa: F401 (register)
+from . import (  # noqa: F401 (register)
+    attention, block, delta_rule, embedding, feedforward, latent_attention, norm, position, routed,
+)
 from .base import (
     Block,
     BuildEnv,

@@ -8,9 +8,9 @@ to its cache.
 
 Categories and what each must provide
 -------------------------------------
-``norm``          ``add_norm(h, delta, ctx, rows=None, tag="norm") -> x``: add ``delta`` to
-                  the 32-bit residual ``h`` in place (unless ``rows`` selects rows, then
-                  nothing is modified) and return the normalised activations.
+``norm``          ``add_norm(h, delta, ctx, rows=None, tag="norm", delta_scale=1.0) -> x``: add
+                  ``delta_scale * delta`` to the 32-bit residual ``h`` in place (unless ``rows``
+                  selects rows, then nothing is modified) and return the normalised activations.
 ``position``      a :class:`PositionEncoding`: ``rotary_table()``/``rotary_dim`` for encodings
                   applied to queries and keys, ``apply_to_embedding`` for additive ones.
 ``mixer``         ``cache_request()`` (what it keeps per request: pages of keys and values,
@@ -18,9 +18,10 @@ Categories and what each must provide
                   ``forward(x, ctx, binding) -> delta`` (32-bit ``[N, hidden]``, or
                   ``[S, N, hidden]`` partial sums that the next norm adds in order).
 ``feed_forward``  ``forward(x, ctx) -> delta`` (32-bit ``[N, hidden]``).
-``block``         the arrangement: ``forward(h, delta, ctx, binding) -> delta`` where ``h``
-                  is the residual stream and ``delta`` the not-yet-added output of the
-                  previous block.
+``block``         the arrangement: ``forward(h, delta, ctx, binding, delta_scale=1.0) -> delta``
+                  where ``h`` is the residual stream and ``delta`` the not-yet-added output of
+                  the previous block, to be added times ``delta_scale``; ``residual_mult`` is the
+                  factor its own returned delta is to be added with.
 ``embedding``     ``forward(token_ids, ctx) -> h`` (32-bit residual stream).
 ``head``          ``forward(x, ctx) -> logits`` (32-bit ``[rows, vocab]``).
 """
@@ -55,6 +56,9 @@ class PagedKVRequest:
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    # Size of a cached value row: None = as large as a key row; 0 = no value rows are kept (a
+    # mixer whose values are a part of its key rows, such as a shared latent vector).
+    value_dim: int | None = None
 
 
 @dataclass(frozen=True)
@@ -140,7 +144,7 @@ class FeedForward(Part):
 class Norm(Part):
     category = "norm"
 
-    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm"):
+    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm", delta_scale: float = 1.0):
         raise NotImplementedError
 
 
@@ -148,6 +152,7 @@ class Block(Part):
     category = "block"
 
     mixer: Mixer
+    residual_mult: float = 1.0  # the factor with which the returned delta enters the residual stream
 
-    def forward(self, h, delta, ctx, binding: CacheBinding | None):
+    def forward(self, h, delta, ctx, binding: CacheBinding | None, delta_scale: float = 1.0):
         raise NotImplementedError

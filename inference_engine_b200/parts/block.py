@@ -1,7 +1,8 @@
 """Arrangements of a layer's parts.
 
-``prenorm_residual`` (engine/model/layers.py:301-303): ``h = x + mixer(norm(x))``, then
-``out = h + feed_forward(norm(h))``.  The residual stream ``h`` is 32-bit and is updated in
+``prenorm_residual`` (engine/model/layers.py:301-303): ``h = x + m * mixer(norm(x))``, then
+``out = h + m * feed_forward(norm(h))``; ``m`` is the parameter ``residual_mult`` (1 unless the
+model description says otherwise), and a layer without a feed-forward stops after its mixer.  The residual stream ``h`` is 32-bit and is updated in
 place; each add is fused into the norm that follows it, so a block returns its
 feed-forward's output as a pending ``delta`` for the next norm to add.
 """
@@ -14,24 +15,30 @@ from .registry import build_part, register_part
 
 @register_part("block", "prenorm_residual")
 class PreNormResidualBlock(Block):
-    def __init__(self, mixer, feed_forward, pre_mixer, pre_feed_forward) -> None:
+    def __init__(self, mixer, feed_forward, pre_mixer, pre_feed_forward, residual_mult: float = 1.0) -> None:
         self.mixer, self.feed_forward = mixer, feed_forward
         self.pre_mixer, self.pre_feed_forward = pre_mixer, pre_feed_forward
+        self.residual_mult = float(residual_mult)
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, *, layer, **_):
+        has_ff = layer.feed_forward is not None
         return cls(
             build_part("mixer", layer.mixer, env),
-            build_part("feed_forward", layer.feed_forward, env),
+            build_part("feed_forward", layer.feed_forward, env) if has_ff else None,
             build_part("norm", layer.norms["pre_mixer"], env),
-            build_part("norm", layer.norms["pre_feed_forward"], env),
+            build_part("norm", layer.norms["pre_feed_forward"], env) if has_ff else None,
+            params.get("residual_mult", 1.0),
         )
 
     def parts(self):
-        return [self.pre_mixer, self.mixer, self.pre_feed_forward, self.feed_forward]
+        both = [self.pre_mixer, self.mixer, self.pre_feed_forward, self.feed_forward]
+        return [p for p in both if p is not None]
 
-    def forward(self, h, delta, ctx, binding: CacheBinding | None):
-        x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer")
+    def forward(self, h, delta, ctx, binding: CacheBinding | None, delta_scale: float = 1.0):
+        x = self.pre_mixer.add_norm(h, delta, ctx, tag="norm.mixer", delta_scale=delta_scale)
         mixed = self.mixer.forward(x, ctx, binding)
-        x = self.pre_feed_forward.add_norm(h, mixed, ctx, tag="norm.ffn")
+        if self.feed_forward is None:
+            return mixed
+        x = self.pre_feed_forward.add_norm(h, mixed, ctx, tag="norm.ffn", delta_scale=self.residual_mult)
         return self.feed_forward.forward(x, ctx)

@@ -2,7 +2,7 @@
 
 Embedding: ``x = table[token_ids]`` with no scaling (engine/model/llama.py:25,61); the rows
 are widened to the 32-bit residual stream.  Head: ``logits = x @ W^T`` in 32-bit out, no
-bias (engine/model/llama.py:36,68); with tied embeddings ``W`` is the embedding table
+bias (engine/model/llama.py:36,68), times ``logit_scale`` where a model has one; with tied embeddings ``W`` is the embedding table
 itself (engine/model/loader.py:91-92), one buffer.
 """
 
@@ -42,14 +42,17 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     category = "head"
 
-    def __init__(self, weight: str | None, vocab_size: int, hidden_size: int, dtype) -> None:
+    def __init__(self, weight: str | None, vocab_size: int, hidden_size: int, dtype,
+                 logit_scale: float = 1.0) -> None:
         self.weight_name, self.vocab_size, self.hidden_size = weight, vocab_size, hidden_size
         self.dtype, self.weight = dtype, None
+        self.logit_scale = float(logit_scale)  # the 32-bit logits are multiplied by it
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
         # weight=None means tied: the model hands over the embedding table at bind time.
-        return cls(params.get("weight"), params["vocab_size"], env.hidden_size, env.torch_dtype)
+        return cls(params.get("weight"), params["vocab_size"], env.hidden_size, env.torch_dtype,
+                   params.get("logit_scale", 1.0))
 
     def weights(self) -> dict[str, WeightDecl]:
         if self.weight_name is None:
@@ -67,4 +70,7 @@ class LinearHead(Part):
         import torch
 
         logits = ctx.ws.buffer("logits", x.shape[0], self.vocab_size, torch.float32, rows_cap=None)
-        return ctx.ops.linear(x, self.weight, logits, tag="head")
+        ctx.ops.linear(x, self.weight, logits, tag="head")
+        if self.logit_scale != 1.0:
+            ctx.ops.scale_(logits, self.logit_scale)
+        return logits

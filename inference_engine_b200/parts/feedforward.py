@@ -56,3 +56,37 @@ class SwiGLU(FeedForward):
         act = ctx.ops.gated_linear(x, self.w_gate_up, self.interleave, ws=ctx.ws, tag="ffn", out_dtype=self.dtype)
         return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
                               allow_split=True)
+
+
+@register_part("feed_forward", "relu2")
+class SquaredReluFF(FeedForward):
+    """Dense feed-forward without a gate: ``down(relu(up(x))^2)``.  The activation is evaluated in
+    32-bit on the product's output and rounded once to the compute dtype."""
+
+    def __init__(self, *, up_proj: str, down_proj: str, hidden_size: int, intermediate_size: int, dtype) -> None:
+        self.names = {"up": up_proj, "down": down_proj}
+        self.hidden_size, self.intermediate_size, self.dtype = hidden_size, intermediate_size, dtype
+        self.w_up = self.w_down = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(up_proj=params["up_proj"], down_proj=params["down_proj"],
+                   hidden_size=params.get("hidden_size", env.hidden_size),
+                   intermediate_size=params["intermediate_size"], dtype=env.torch_dtype)
+
+    def weights(self) -> dict[str, WeightDecl]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.names["up"]: WeightDecl((i, h)), self.names["down"]: WeightDecl((h, i))}
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        self.w_up = tensors[self.names["up"]].to(self.dtype).contiguous()
+        self.w_down = tensors[self.names["down"]].to(self.dtype).contiguous()
+
+    def forward(self, x, ctx):
+        import torch
+
+        up = ctx.ops.linear(x, self.w_up, ws=ctx.ws, tag="ffn.up", out_dtype=self.dtype)
+        act = ctx.ws.buffer("ffn.act", x.shape[0], self.intermediate_size, self.dtype)
+        ctx.ops.relu_squared(up, act)
+        return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
+                              allow_split=True)

@@ -28,8 +28,39 @@ class RMSNorm(Norm):
     def bind(self, tensors, env: BuildEnv) -> None:
         self.weight = tensors[self.weight_name].float().contiguous()
 
-    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm"):
+    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm", delta_scale: float = 1.0):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buffer(tag, n, self.size, self.dtype)
-        ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        if delta_scale == 1.0:
+            ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        else:
+            ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows, delta_scale=float(delta_scale))
+        return out
+
+
+@register_part("norm", "layer")
+class LayerNorm(Norm):
+    """Layer norm over the last dimension with a weight and no bias, the residual add fused in:
+    ``(x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight``, all in 32-bit on the 32-bit
+    residual stream; the result is rounded once to the compute dtype."""
+
+    def __init__(self, weight: str, size: int, eps: float, dtype) -> None:
+        self.weight_name, self.size, self.eps, self.dtype = weight, int(size), float(eps), dtype
+        self.weight = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(params["weight"], params.get("size", env.hidden_size), params["eps"],
+                   env.torch_dtype)
+
+    def weights(self) -> dict[str, WeightDecl]:
+        return {self.weight_name: WeightDecl((self.size,), "vector", "ones_plus_normal")}
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        self.weight = tensors[self.weight_name].float().contiguous()
+
+    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm", delta_scale: float = 1.0):
+        n = h.shape[0] if rows is None else rows.shape[0]
+        out = ctx.ws.buffer(tag, n, self.size, self.dtype)
+        ctx.ops.layernorm(h, delta, self.weight, self.eps, out, rows, delta_scale=float(delta_scale))
         return out

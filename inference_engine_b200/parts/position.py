@@ -1,5 +1,7 @@
 """Position encodings.
 
+``learned``: a table of vectors added to the embedding.
+
 ``rotary``: rotation of query and key halves by position-dependent angles, with the
 optional Llama 3 frequency scaling.  Frequencies follow engine/model/layers.py:55-73 and
 angles engine/model/layers.py:75-79: everything is 32-bit; the table holds cos and sin of
@@ -37,10 +39,17 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling: dict | None):
 
 @register_part("position", "rotary")
 class RotaryEncoding(PositionEncoding):
+    LAYOUTS = ("halves", "interleaved")
+
     def __init__(self, rotary_dim: int, theta: float, scaling: dict | None,
-                 max_positions: int) -> None:
+                 max_positions: int, layout: str = "halves") -> None:
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim ({rotary_dim}) must be even")
+        if layout not in self.LAYOUTS:
+            raise ValueError(f"rotary layout {layout!r} is not one of {self.LAYOUTS}")
+        # which entries form the pair rotated by angle j: "halves": j and j + rotary_dim/2 (Llama's);
+        # "interleaved": 2j and 2j + 1.  The table of angles is the same; the consumer reads `layout`.
+        self.layout = layout
         self.rotary_dim, self.theta, self.scaling = int(rotary_dim), float(theta), scaling
         self.max_positions = int(max_positions)
         self.inv_freq = self._table = None
@@ -48,7 +57,7 @@ class RotaryEncoding(PositionEncoding):
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
         return cls(params["rotary_dim"], params["theta"], params.get("scaling"),
-                   env.max_positions)
+                   env.max_positions, params.get("layout", "halves"))
 
     def bind(self, tensors, env: BuildEnv) -> None:
         """No stored tensor (the reference keeps ``inv_freq`` out of checkpoints,
@@ -62,6 +71,31 @@ class RotaryEncoding(PositionEncoding):
 
     def rotary_table(self):
         return self._table
+
+
+@register_part("position", "learned")
+class LearnedPositions(PositionEncoding):
+    """A learned vector per position, added (unscaled) to the embedded tokens in the 32-bit
+    residual stream.  The table's rows bound the positions a request can reach."""
+
+    def __init__(self, weight: str, positions: int, hidden_size: int) -> None:
+        self.weight_name, self.positions, self.hidden_size = weight, int(positions), int(hidden_size)
+        self.table = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(params["weight"], params["positions"], params.get("hidden_size", env.hidden_size))
+
+    def weights(self):
+        from .base import WeightDecl
+
+        return {self.weight_name: WeightDecl((self.positions, self.hidden_size), "table")}
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        self.table = tensors[self.weight_name].to(env.torch_dtype).contiguous()
+
+    def apply_to_embedding(self, h, ctx) -> None:
+        ctx.ops.add_position_rows(h, self.table, ctx.positions)
 
 
 @register_part("position", "none")

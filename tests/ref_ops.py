@@ -17,19 +17,156 @@ class RefOps:
     def embedding(self, table, ids, out):
         out.copy_(table[ids.long()].float())
 
-    def rmsnorm(self, h, delta, weight, eps, out, rows=None):
+    @staticmethod
+    def _added(h, delta, rows, delta_scale):
         if delta is not None and delta.dim() == 3:  # the parts of a split matrix product
             delta = delta.sum(0)
         if rows is None:
             if delta is not None:
-                h.add_(delta)
-            x = h
-        else:
-            x = h[rows.long()]
-            if delta is not None:
-                x = x + delta[rows.long()]
+                h.add_(delta * delta_scale)
+            return h
+        x = h[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()] * delta_scale
+        return x
+
+    def rmsnorm(self, h, delta, weight, eps, out, rows=None, delta_scale=1.0):
+        x = self._added(h, delta, rows, delta_scale)
         normed = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
         out.copy_((weight * normed).to(out.dtype))
+
+    def layernorm(self, h, delta, weight, eps, out, rows=None, delta_scale=1.0):
+        x = self._added(h, delta, rows, delta_scale)
+        centred = x - x.mean(-1, keepdim=True)
+        out.copy_((centred * torch.rsqrt(centred.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def add_position_rows(self, h, table, positions):
+        h.add_(table[positions.long()].float())
+
+    def relu_squared(self, x, out):
+        out.copy_(torch.relu(x.float()).pow(2).to(out.dtype))
+
+    def scale_(self, t, factor):
+        t.mul_(factor)
+
+    # --- latent attention ---------------------------------------------------------------------
+
+    def latent_prep(self, proj, positions, table, rot_dims, norm_w, eps, q_plain, q_abs, gate, cache,
+                    slot_mapping, heads, dim, rot_dim, rank, page_size):
+        n = proj.shape[0]
+        row = rank + rot_dim
+        q = proj[:, : heads * (dim + rot_dim)].reshape(n, heads, dim + rot_dim).float()
+        dkv = proj[:, heads * (dim + rot_dim): heads * (dim + rot_dim) + row].float()
+        g = proj[:, heads * (dim + rot_dim) + row:].float()
+
+        def rot(x):  # [n, ..., rot_dim]
+            if table is None or rot_dims == 0:
+                return x
+            cos, sin = table[positions.long(), 0], table[positions.long(), 1]  # [n, rot_dims/2]
+            while cos.dim() < x.dim():
+                cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+            out = x.clone()
+            u, v = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2]
+            out[..., 0:rot_dims:2] = u * cos - v * sin
+            out[..., 1:rot_dims:2] = v * cos + u * sin
+            return out
+
+        q_plain.copy_(q[..., :dim].reshape(n, heads * dim).to(q_plain.dtype))
+        q_abs.view(n, heads, row)[:, :, rank:] = rot(q[..., dim:]).to(q_abs.dtype)
+        gate.copy_(torch.sigmoid(g))
+        if slot_mapping is not None:
+            c = dkv[:, :rank]
+            c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * norm_w
+            rows = torch.cat([c, rot(dkv[:, rank:])], dim=-1).to(cache.dtype)
+            slots = slot_mapping.long()
+            cache[slots // page_size, 0, slots % page_size] = rows
+
+    def headwise_linear(self, x, w, out, row_scale=None):
+        y = torch.einsum("nhk,hok->nho", x.float(), w.float())
+        if row_scale is not None:
+            y = y * row_scale[..., None]
+        out.copy_(y.to(out.dtype))
+
+    # --- delta rule ---------------------------------------------------------------------------
+
+    def delta_prep(self, qkvb, a, conv_w, A_log, dt_bias, state, slots, ctx, q_out, k_out, v_out, beta,
+                   decay, heads, kv_heads, dim, vdim, taps):
+        channels = conv_w.shape[0]
+        matrix = heads * dim * vdim
+        qk = kv_heads * dim
+        slot_list = slots.tolist()
+        for start, n, slot in zip(ctx.q_starts, ctx.q_lens, slot_list):
+            if n == 0:
+                continue
+            tail = state[slot, matrix:].view(taps - 1, channels)
+            x = torch.cat([tail, qkvb[start: start + n, :channels].float()])  # [taps - 1 + n, channels]
+            y = torch.zeros(n, channels)
+            for j in range(taps):
+                y += x[j: j + n] * conv_w[:, j]
+            y = y * torch.sigmoid(y)
+            q = y[:, :qk].view(n, kv_heads, dim)
+            k = y[:, qk: 2 * qk].view(n, kv_heads, dim)
+            q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+            k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+            q_out[start: start + n] = q.reshape(n, qk)
+            k_out[start: start + n] = k.reshape(n, qk)
+            v_out[start: start + n] = y[:, 2 * qk:]
+            state[slot, matrix:] = x[n:].reshape(-1)
+        beta.copy_(torch.sigmoid(qkvb[:, channels:].float()))
+        rate = torch.exp(A_log)[None, :, None]
+        soft = torch.nn.functional.softplus(a.float() + dt_bias).view(-1, heads, dim)
+        decay.copy_(torch.exp(-rate * soft).reshape(decay.shape))
+
+    def delta_rule(self, q, k, v, beta, decay, state, slots, ctx, out, heads, kv_heads, dim, vdim):
+        rep = heads // kv_heads
+        matrix = heads * dim * vdim
+        for start, n, slot in zip(ctx.q_starts, ctx.q_lens, slots.tolist()):
+            if n == 0:
+                continue
+            S = state[slot, :matrix].view(heads, vdim, dim).transpose(1, 2).clone()  # [heads, dim, vdim]
+            for t in range(start, start + n):
+                kt = k[t].view(kv_heads, dim).repeat_interleave(rep, 0)
+                qt = q[t].view(kv_heads, dim).repeat_interleave(rep, 0)
+                S = decay[t].view(heads, dim)[:, :, None] * S
+                u = beta[t][:, None] * (v[t].view(heads, vdim) - torch.einsum("hdv,hd->hv", S, kt))
+                S = S + kt[:, :, None] * u[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, qt).reshape(-1)
+            state[slot, :matrix] = S.transpose(1, 2).reshape(-1)
+
+    def gated_rms_heads(self, o, weight, eps, gate_pre, out, heads, vdim):
+        x = o.view(-1, heads, vdim)
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+        y = y * torch.sigmoid(gate_pre.float().view(-1, heads, vdim))
+        out.copy_(y.reshape(out.shape).to(out.dtype))
+
+    # --- routed experts -----------------------------------------------------------------------
+
+    def route_topk(self, x, w_router, groups, keep, ids, weights):
+        n, experts, top = x.shape[0], w_router.shape[0], ids.shape[1]
+        s = (x.float() @ w_router.t()).softmax(-1)
+        per = experts // groups
+        best = s.view(n, groups, per).max(-1).values
+        allowed = torch.zeros(n, groups, dtype=torch.bool)
+        allowed.scatter_(1, best.topk(keep, dim=-1).indices, True)
+        allowed = allowed[:, :, None].expand(-1, -1, per).reshape(n, experts)
+        chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
+        w = s.gather(1, chosen)
+        ids.copy_(chosen.to(ids.dtype))
+        weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20))
+
+    def routed_experts(self, x, ids, weights, w_gate_up, w_down, *, limit, alpha, up_offset, ws, tag="moe"):
+        n, top = ids.shape
+        out = ws.buffer(tag + ".delta", top * n, w_down.shape[1], torch.float32).view(top, n, -1)
+        xf = x.float()
+        for t in range(n):
+            for j in range(top):
+                e = int(ids[t, j])
+                g, u = xf[t] @ w_gate_up[e, 0].float().t(), xf[t] @ w_gate_up[e, 1].float().t()
+                if limit is not None:
+                    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+                y = (g * torch.sigmoid(alpha * g) * (u + up_offset)).to(x.dtype).float()
+                out[j, t] = weights[t, j] * (y @ w_down[e].float().t())
+        return out
 
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         if out is None:
@@ -63,7 +200,8 @@ class RefOps:
             v_cache[page, :, offset] = v.to(v_cache.dtype)
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
-                        scale, window, out, ragged=None):
+                        scale, window, out, ragged=None, value_dim=None):
+        vd = hd if value_dim is None else value_dim  # value rows: the first `vd` entries of v_cache's rows
         groups = nh // nkv
         tables = block_tables.long().cpu()
         positions = ctx.positions.cpu().tolist()
@@ -75,13 +213,13 @@ class RefOps:
             pages = tables[s][keys // page_size].to(k_cache.device)
             offs = (keys % page_size).to(k_cache.device)
             k = k_cache[pages, :, offs].float()  # [keys, nkv, hd]
-            v = v_cache[pages, :, offs].float()
+            v = v_cache[pages, :, offs].float()[..., :vd]
             k = k.repeat_interleave(groups, dim=1)
             v = v.repeat_interleave(groups, dim=1)
             qt = q[t].reshape(nh, hd).float()
             scores = torch.einsum("hd,khd->hk", qt, k) * scale
             probs = scores.softmax(-1)
-            out[t] = torch.einsum("hk,khd->hd", probs, v).reshape(nh * hd).to(out.dtype)
+            out[t] = torch.einsum("hk,khd->hd", probs, v).reshape(nh * vd).to(out.dtype)
 
     def silu_mul(self, gate_up, out, interleave=0):
         if gate_up.dim() == 3:
