@@ -413,6 +413,133 @@ def run_ours(args) -> dict:
     }
 
 
+# --- another design beside the closest model the engine already had ------------------------------
+
+DESIGN_SIZES = {
+    # width, (latent: heads, dim, rot_dim, vdim, kv_rank), (delta: heads, kv_heads, dim, vdim, taps),
+    # dense ff, (experts: ff, count, top, groups, kept groups), low ranks
+    "w1024": (1024, (8, 64, 32, 64, 256), (8, 8, 64, 64, 4), 4096, (512, 16, 4, 4, 2), 32),
+    "w2048": (2048, (16, 128, 64, 128, 512), (16, 16, 128, 128, 4), 8192, (1024, 32, 4, 4, 2), 64),
+}
+DESIGN_VOCAB, DESIGN_PROMPT = 32000, 1024
+
+
+def rugedra_config(size: str) -> dict:
+    width, la, de, ff, ex, rank = DESIGN_SIZES[size]
+    latent = {"heads": la[0], "dim": la[1], "rot_dim": la[2], "vdim": la[3], "kv_rank": la[4],
+              "scale": (la[1] + la[2]) ** -0.5, "rot": {"base": 10000.0, "dims": la[2]}}
+    delta = {"heads": de[0], "kv_heads": de[1], "dim": de[2], "vdim": de[3], "conv": de[4],
+             "decay_rank": rank, "gate_rank": rank}
+    moe = {"kind": "moe", "expert": {"ff": ex[0], "limit": 7.0},
+           "router": {"experts": ex[1], "top": ex[2], "groups": {"count": ex[3], "keep": ex[4]}}}
+    dense = {"kind": "dense", "ff": ff}
+    layers = [("latent_attention", latent, dense), ("channel_delta", delta, moe),
+              ("latent_attention", latent, moe), ("channel_delta", delta, dense)]
+    return {"architecture": "Rugedra", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
+            "norm": {"eps": 1e-5}, "residual_mult": 0.7, "logit_scale": 0.5,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+
+
+def llama_config_like(size: str) -> dict:
+    width, _, _, ff, _, _ = DESIGN_SIZES[size]
+    cfg = dict(LLAMA_1B)
+    cfg.update(num_hidden_layers=4, hidden_size=width, num_attention_heads=width // 64,
+               num_key_value_heads=max(width // 256, 1), head_dim=64, intermediate_size=ff,
+               vocab_size=DESIGN_VOCAB, tie_word_embeddings=False, max_position_embeddings=MAX_CONTEXT)
+    return cfg
+
+
+def design_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, ctx: float, decode: bool) -> dict:
+    """Per kind of kernel of the Rugedra model: microseconds per launch and, where the kind has such a
+    figure, what it is of the measured peak: decode launches against the copy rate for the bytes they
+    must read (weights, cached rows, state), prompt launches against the burst bf16 rate for their
+    flops (the recurrence and the 32-bit stages: against nothing, the time only)."""
+    width, la, de, ff, ex, rank = DESIGN_SIZES[size]
+    H, dim, rot, vdim, kvr = la
+    row = kvr + rot
+    dh, dkv, ddim, dvd, taps = de
+    eff, experts, top = ex[0], ex[1], ex[2]
+    weights = {  # elements of the matrices a launch reads
+        "linear:latent.in": width * (H * (dim + rot) + row + H), "linear:mixer.delta": None,
+        "linear:delta.in": width * (2 * dkv * ddim + dh * dvd + dh), "linear:ffn.up": width * ff,
+        "linear:ffn.delta": width * ff, "linear:head": width * DESIGN_VOCAB,
+        "latent.headwise": H * kvr * (dim + vdim) // 2,  # (two launches per layer, averaged)
+        "routed.gate_up": 2 * eff * width * min(experts, batch * top if decode else experts),
+        "routed.down": eff * width * min(experts, batch * top if decode else experts),
+    }
+    flops = {  # per prompt launch
+        "attention.latent": 2.0 * tokens * tokens / 2 * H * (row + kvr),
+        "routed.gate_up": 2.0 * tokens * top * 2 * eff * width, "routed.down": 2.0 * tokens * top * eff * width,
+        "latent.headwise": 2.0 * tokens * H * kvr * (dim + vdim) / 2,
+    }
+    rows = {}
+    for kind, r in kinds.items():
+        us = r["ms"] / r["launches"] * 1e3
+        out = {"us": round(us, 2), "launches": r["launches"]}
+        if decode:
+            nbytes = None
+            if weights.get(kind):
+                nbytes = 2 * weights[kind]
+            elif kind == "attention.latent":
+                nbytes = batch * ctx * row * 2
+            elif kind == "delta.rule":
+                nbytes = batch * dh * ddim * dvd * 4 * 2
+            if nbytes:
+                out.update(gbs=round(nbytes / (us * 1e-6) / 1e9, 1),
+                           frac=round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3))
+        else:
+            f = flops.get(kind) or (2.0 * tokens * weights[kind] if weights.get(kind) and kind != "linear:head" else None)
+            if f:
+                out.update(tflops=round(f / (us * 1e-6) / 1e12, 1),
+                           frac=round(f / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4))
+        rows[kind] = out
+    return rows
+
+
+def run_design(args) -> dict:
+    """`--design rugedra`: prompt and decode throughput of the Rugedra design at layer sizes of a real
+    model's (four layers: latent attention + dense, delta rule + experts, latent attention + experts,
+    delta rule + dense; random weights), beside a Llama model of the same width, depth, feed-forward
+    size and vocabulary, and every kind of kernel of both by itself."""
+    import torch
+
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+
+    global PROMPT_LEN
+    PROMPT_LEN = DESIGN_PROMPT
+    peaks, peaks_kind = measured_peaks()
+    torch.cuda.set_device(0)
+    steps, batch = min(args.steps, 128), args.batch
+    tokens_needed = batch * (PROMPT_LEN + args.warmup + steps + 64) + 4 * PREFILL_LEN
+    sampler = ClockSampler()
+    sampler.start()
+    out = {}
+    for size in args.sizes.split(","):
+        for name, cfg in (("rugedra", rugedra_config(size)), ("llama", llama_config_like(size))):
+            engine = LLMEngine.from_random(
+                cfg, seed=0, dtype="bfloat16", device="cuda", max_model_len=MAX_CONTEXT,
+                num_blocks=-(-tokens_needed // BLOCK_SIZE), block_size=BLOCK_SIZE, max_num_seqs=max(batch, 8),
+                max_num_batched_tokens=4 * PROMPT_LEN)
+            tps, ms_step, ctx, launches, kinds = decode_device_timed(engine, batch, steps, args.warmup, 1, breakdown=True)
+            prefill_ms, kinds_prefill = prefill_timed(engine)
+            row = {"decode_tokens_per_s": round(tps, 1), "decode_ms_per_step": round(ms_step, 4),
+                   "decode_captured": engine.graphs is not None, "gpu_launches": int(launches),
+                   "prefill_tokens_per_s": round(PREFILL_LEN / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3)}
+            if name == "rugedra":
+                row["kernels"] = {f"decode_b{batch}": design_rows(size, kinds, peaks, batch, batch, ctx, True),
+                                  f"prefill_{PREFILL_LEN}": design_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
+            else:
+                row["kernels"] = {f"decode_b{batch}": kernel_rows(cfg, kinds, peaks, batch, batch, ctx, True),
+                                  f"prefill_{PREFILL_LEN}": kernel_rows(cfg, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
+            out[f"{name}_{size}"] = row
+            del engine
+            torch.cuda.empty_cache()
+    return {"design": "rugedra", "beside": "llama of equal width, depth, feed-forward size and vocabulary",
+            "batch": batch, "decode_context": PROMPT_LEN, "prefill_tokens": PREFILL_LEN, "dtype": "bf16",
+            "data": "synthetic: seeded random weights N(0, 0.02), uniform-random token ids",
+            "peaks": peaks_kind, "models": out, "clocks": sampler.stop()}
+
+
 # --- the reference --------------------------------------------------------------------------------
 
 
@@ -529,12 +656,19 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--design", default=None, choices=["rugedra"],
+                    help="instead of the default workload: this design at real layer sizes beside the closest "
+                         "model the engine had, prompt and decode throughput and every kind of kernel")
+    ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of " + ",".join(DESIGN_SIZES))
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design is not None:
+        print(json.dumps(run_design(args)))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0

@@ -142,12 +142,15 @@ class DecodeGraphs:
             ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=width)
         if not captured:
             # Run once outside a capture (buffers get allocated, libraries initialised) ...
+            # (per-request state must not move twice: what this run does to it is undone)
+            kept = runner.keep_state(ctx)
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
                 runner.model.forward(ctx, rows)
             torch.cuda.current_stream().wait_stream(stream)
             torch.cuda.synchronize()
+            runner.restore_state(kept)
             if self._version != runner.ws.version:
                 self._graphs.clear()
                 self._version = runner.ws.version
@@ -158,6 +161,7 @@ class DecodeGraphs:
             logits = _capture(torch, graph, lambda: runner.model.forward(ctx, rows))
             self._graphs[key] = (graph, logits, getattr(runner.ops, "launches", 0) - before)
         graph, logits, _ = self._graphs[key]
+        runner.reset_fresh_entries(entries)
         graph.replay()
         self.replays += 1
         return logits[: len(entries)]
@@ -233,12 +237,15 @@ class MixedGraphs:
             raise RuntimeError(f"a step packed for {ctx.bounds} cannot replay the launch captured for {key}")
         if key not in self._graphs:
             # Run once outside a capture (buffers get allocated, libraries initialised) ...
+            # (per-request state must not move twice: what this run does to it is undone)
+            kept = runner.keep_state(ctx)
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(stream):
                 runner.model.forward(ctx, rows)
             torch.cuda.current_stream().wait_stream(stream)
             torch.cuda.synchronize()
+            runner.restore_state(kept)
             if self._version != runner.ws.version:
                 self._graphs.clear()
                 self._version = runner.ws.version
@@ -248,6 +255,7 @@ class MixedGraphs:
             logits = _capture(torch, graph, lambda: runner.model.forward(ctx, rows))
             self._graphs[key] = (graph, logits)
         graph, logits = self._graphs[key]
+        runner.reset_fresh_entries(entries)
         graph.replay()
         self.replays += 1
         return logits[:wanted] if wanted else None

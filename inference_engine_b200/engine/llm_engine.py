@@ -80,9 +80,9 @@ class LLMEngine:
                                    config.enable_chunked_prefill)
         self.sampler = Sampler(ops, self.device, model.spec.vocab_size)
         use_graphs = config.enable_cuda_graphs
-        if use_graphs is None:  # where they can be captured: on a GPU, no per-request state slots
+        if use_graphs is None:  # where they can be captured: on a GPU, with parts that say they can be
             use_graphs = (str(self.device).startswith("cuda") and torch.cuda.is_available()
-                          and not model.state_groups)
+                          and getattr(model, "captures", True))
         self.graphs = DecodeGraphs(self.runner, max_num_seqs, table_width) if use_graphs else None
         use_mixed = config.enable_mixed_graphs
         if use_mixed is None:

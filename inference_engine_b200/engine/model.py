@@ -46,6 +46,11 @@ class Model:
         yield from _walk(self.final_norm)
         yield from _walk(self.head)
 
+    @property
+    def captures(self) -> bool:
+        """Whether every part's step can be captured as a launch sequence."""
+        return all(getattr(part, "captures", True) for part in self.all_parts())
+
     def declared_weights(self) -> dict[str, WeightDecl]:
         out: dict[str, WeightDecl] = {}
         for part in self.all_parts():

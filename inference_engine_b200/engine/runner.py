@@ -442,6 +442,32 @@ class ModelRunner:
         for st in self.storage.state:
             st.index_fill_(1, index, 0.0)
 
+    def reset_fresh_entries(self, entries: list[StepEntry]) -> None:
+        """The same from the entries themselves (for steps that replay a captured launch sequence:
+        the zeroing is launched ahead of the replay, in stream order)."""
+        if not self.storage.state:
+            return
+        slots = [self.cache.state_slot(e.req_id) for e in entries if e.start == 0]
+        if slots:
+            index = self._torch.tensor(slots, dtype=self._torch.long, device=self.device)
+            for st in self.storage.state:
+                st.index_fill_(1, index, 0.0)
+
+    def keep_state(self, ctx: StepContext):
+        """Copies of the state rows the step's requests hold (None without state groups), for a
+        step that is run twice: a warm-up run before its launches are captured."""
+        if not self.storage.state:
+            return None
+        slots = sorted(set(ctx.groups[len(self.storage.paged)].slots_host))
+        index = self._torch.tensor(slots, dtype=self._torch.long, device=self.device)
+        return index, [st.index_select(1, index) for st in self.storage.state]
+
+    def restore_state(self, kept) -> None:
+        if kept is not None:
+            index, rows = kept
+            for st, saved in zip(self.storage.state, rows):
+                st.index_copy_(1, index, saved)
+
     def step(self, entries: list[StepEntry]):
         """Run the entries as one batch; return ``[wanted, vocab]`` 32-bit logits in the order
         of the entries and of their ``want`` lists, or None when nothing is wanted."""

@@ -98,6 +98,10 @@ class BuildEnv:
 
 class Part:
     category = "part"
+    # Whether the part's step is a fixed sequence of kernel launches that reads lengths, slots and
+    # tables from device memory, so that it can be captured once and replayed (a part that loops over
+    # requests on the host, or reads device values there, says False).
+    captures = True
 
     def weights(self) -> dict[str, WeightDecl]:
         """Full tensor names this part reads, with their shapes."""

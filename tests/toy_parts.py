@@ -25,6 +25,8 @@ from tests import plain_llama as P
 
 
 class ToyStateMixer(Mixer):
+    captures = False  # (it walks the requests on the host)
+
     def __init__(self, prefix: str, hidden: int, width: int) -> None:
         self.prefix, self.hidden, self.width = prefix, hidden, width
 
@@ -63,6 +65,8 @@ class ToyStateMixer(Mixer):
 
 
 class ToyRoutedFeedForward(FeedForward):
+    captures = False  # (it reads the routing on the host)
+
     def __init__(self, prefix: str, hidden: int, inter: int, experts: int) -> None:
         self.prefix, self.hidden, self.inter, self.experts = prefix, hidden, inter, experts
 
