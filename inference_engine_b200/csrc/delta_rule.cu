@@ -25,9 +25,11 @@ __device__ __forceinline__ float silu_f(float y) { return y / (1.0f + expf(-y));
 __device__ __forceinline__ float sigmoid_f(float y) { return 1.0f / (1.0f + expf(-y)); }
 __device__ __forceinline__ float softplus_f(float y) { return y > 20.0f ? y : log1pf(expf(y)); }
 
-// One block per token.  channels = 2 * kv_heads * dim + heads * vdim; qkvb rows hold the channels
-// and then `heads` betas.
-__global__ void __launch_bounds__(256)
+// grid: (tokens, units).  The units of a token: the q heads, the k heads (convolution, silu, unit
+// norm over `dim` channels each), the v heads (convolution and silu over `vdim` channels each), the
+// heads' decays (`dim` values each), and one unit for the betas.  channels = 2 * kv_heads * dim +
+// heads * vdim; qkvb rows hold the channels and then `heads` betas.
+__global__ void __launch_bounds__(128)
 delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restrict__ a,
                   const float* __restrict__ conv_w, const float* __restrict__ A_log,
                   const float* __restrict__ dt_bias, const float* __restrict__ state, long long state_stride,
@@ -35,10 +37,25 @@ delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restric
                   const int* __restrict__ cu_q, float* __restrict__ q_out, float* __restrict__ k_out,
                   float* __restrict__ v_out, float* __restrict__ beta, float* __restrict__ decay,
                   int heads, int kv_heads, int dim, int vdim, int taps, int num_slots, int* err) {
-    extern __shared__ float y[];  // [2 * kv_heads * dim]: q and k after the convolution
+    extern __shared__ float y[];  // [max(dim, vdim)]: one unit's channels after the convolution
+    __shared__ float red[4];
     ie_pdl_trigger();
     ie_pdl_wait();
-    int n = blockIdx.x, tid = threadIdx.x;
+    int n = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x;
+    int qk = kv_heads * dim, channels = 2 * qk + heads * vdim;
+    if (unit == 2 * kv_heads + 2 * heads) {  // the betas
+        for (int h = tid; h < heads; h += blockDim.x) beta[(size_t)n * heads + h] = sigmoid_f(qkvb[(size_t)n * ld + channels + h]);
+        return;
+    }
+    if (unit >= 2 * kv_heads + heads) {  // a head's decays
+        int h = unit - 2 * kv_heads - heads;
+        float rate = expf(A_log[h]);
+        for (int d = tid; d < dim; d += blockDim.x) {
+            size_t i = (size_t)n * heads * dim + h * dim + d;
+            decay[i] = expf(-rate * softplus_f(a[i] + dt_bias[h * dim + d]));
+        }
+        return;
+    }
     int seq = seq_of_token[n];
     int t = n - cu_q[seq];  // the token's place among the request's tokens of this step
     int slot = slots[seq];
@@ -46,39 +63,33 @@ delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restric
         if (tid == 0) ie_report(err, IE_ERR_PAGE, slot, n);
         return;
     }
-    int qk = kv_heads * dim, channels = 2 * qk + heads * vdim;
+    bool is_v = unit >= 2 * kv_heads;
+    int width = is_v ? vdim : dim;
+    int first = is_v ? 2 * qk + (unit - 2 * kv_heads) * vdim : unit * dim;  // the unit's first channel
     const float* tail = state + (size_t)slot * state_stride + (size_t)heads * dim * vdim;
-    for (int c = tid; c < channels; c += blockDim.x) {
+    float ss = 0.f;
+    for (int i = tid; i < width; i += blockDim.x) {
+        int c = first + i;
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
             int back = taps - 1 - j;  // this tap looks `back` tokens back
-            float x;
-            if (t - back >= 0) x = qkvb[(size_t)(n - back) * ld + c];
-            else x = tail[(size_t)(taps - 1 + t - back) * channels + c];
+            float x = (t - back >= 0) ? qkvb[(size_t)(n - back) * ld + c]
+                                      : tail[(size_t)(taps - 1 + t - back) * channels + c];
             acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
         }
-        float s = silu_f(acc);
-        if (c < 2 * qk) y[c] = s;
-        else v_out[(size_t)n * heads * vdim + (c - 2 * qk)] = s;
+        float sv = silu_f(acc);
+        if (is_v) v_out[(size_t)n * heads * vdim + (c - 2 * qk)] = sv;
+        else { y[i] = sv; ss = fmaf(sv, sv, ss); }
     }
+    if (is_v) return;
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
-    int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
-    for (int hh = warp; hh < 2 * kv_heads; hh += warps) {  // q heads, then k heads
-        const float* src = y + hh * dim;
-        float ss = 0.f;
-        for (int d = lane; d < dim; d += 32) ss = fmaf(src[d], src[d], ss);
-        ss = warp_sum(ss);
-        float f = 1.0f / sqrtf(ss + 1e-6f);
-        bool is_q = hh < kv_heads;
-        if (is_q) f *= 1.0f / sqrtf((float)dim);
-        float* dst = (is_q ? q_out : k_out) + (size_t)n * qk + (is_q ? hh : hh - kv_heads) * dim;
-        for (int d = lane; d < dim; d += 32) dst[d] = src[d] * f;
-    }
-    for (int h = tid; h < heads; h += blockDim.x) beta[(size_t)n * heads + h] = sigmoid_f(qkvb[(size_t)n * ld + channels + h]);
-    for (int i = tid; i < heads * dim; i += blockDim.x) {
-        float rate = expf(A_log[i / dim]);
-        decay[(size_t)n * heads * dim + i] = expf(-rate * softplus_f(a[(size_t)n * heads * dim + i] + dt_bias[i]));
-    }
+    float f = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) + 1e-6f);
+    bool is_q = unit < kv_heads;
+    if (is_q) f *= 1.0f / sqrtf((float)dim);
+    float* dst = (is_q ? q_out : k_out) + (size_t)n * qk + (is_q ? unit : unit - kv_heads) * dim;
+    for (int i = tid; i < dim; i += blockDim.x) dst[i] = y[i] * f;
 }
 
 // One block per request of the step: the kept inputs become the last taps - 1 of (kept, new).
@@ -107,14 +118,29 @@ __global__ void delta_conv_tail_kernel(const float* __restrict__ qkvb, int ld, f
 constexpr int DR_THREADS = 128;
 constexpr int DR_CHUNK = 8;  // tokens staged in shared memory at a time
 
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16f(float* dst, const float* src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
 // grid: (column blocks, heads, requests).  R rows per lane; TPC lanes per column (a power of two).
-template <int R>
+// The tokens' k, q, decay, v and beta come through shared memory eight tokens at a time, the next
+// eight on their way (cp.async, two buffers) while these are worked on.  Rows are padded to
+// R * TPC entries that read as zero, so the inner loops carry no bounds checks.
+template <int R, int TPC>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ state,
                   long long state_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
-                  float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int tpc, int num_slots) {
-    extern __shared__ float sm[];  // per staged token: k[dim], q[dim], g[dim]; then v and beta
+                  float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int num_slots) {
+    extern __shared__ __align__(16) float sm[];  // two buffers of: k, q, g [CHUNK][DP] each, v [CHUNK][COLS], beta [CHUNK]
+    constexpr int COLS = DR_THREADS / TPC, DP = R * TPC;
+    constexpr int BUF = DR_CHUNK * (3 * DP + COLS + 4);
     ie_pdl_trigger();
     ie_pdl_wait();
     int seq = blockIdx.z, head = blockIdx.y;
@@ -122,72 +148,102 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     int slot = slots[seq];
     if (len <= 0 || slot < 0 || slot >= num_slots) return;
     int tid = threadIdx.x;
-    int cols_per_block = DR_THREADS / tpc;
-    int sub = tid % tpc, col = blockIdx.x * cols_per_block + tid / tpc;
+    int sub = tid % TPC, my_col = tid / TPC, col = blockIdx.x * COLS + my_col;
     bool live = col < vdim;
     int kvh = head / (heads / kv_heads);
     float* S = state + (size_t)slot * state_stride + ((size_t)head * vdim + (live ? col : 0)) * dim;
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        int r = sub + i * tpc;
+        int r = sub + i * TPC;
         s[i] = (live && r < dim) ? S[r] : 0.f;
     }
-    float* ks = sm;                          // [CHUNK][dim]
-    float* qs = ks + DR_CHUNK * dim;         // [CHUNK][dim]
-    float* gs = qs + DR_CHUNK * dim;         // [CHUNK][dim]
-    float* vs = gs + DR_CHUNK * dim;         // [CHUNK][cols_per_block]
-    float* bs = vs + DR_CHUNK * cols_per_block;  // [CHUNK]
-    int c0 = blockIdx.x * cols_per_block;
-    for (int t0 = 0; t0 < len; t0 += DR_CHUNK) {
+    if (DP > dim)  // the rows' padding: k and q read as zero there (the copies never touch it)
+        for (int i = tid; i < 2 * DR_CHUNK * 3 * (DP - dim); i += DR_THREADS) {
+            int row = i / (DP - dim), c = dim + i % (DP - dim);  // row: (buffer, array, token)
+            int b = row / (3 * DR_CHUNK), rest = row % (3 * DR_CHUNK);
+            sm[b * BUF + rest * DP + c] = 0.f;
+        }
+    int c0 = blockIdx.x * COLS;
+    bool vec = (dim % 4 == 0) && (vdim % 4 == 0) && (COLS % 4 == 0);
+    auto stage = [&](int t0, int b) {  // the chunk's values on their way into buffer b
         int cnt = min(DR_CHUNK, len - t0);
-        __syncthreads();
-        for (int i = tid; i < cnt * dim; i += DR_THREADS) {
-            int tt = i / dim, d = i - tt * dim;
-            size_t n = (size_t)(start + t0 + tt);
-            ks[i] = k[(n * kv_heads + kvh) * dim + d];
-            qs[i] = q[(n * kv_heads + kvh) * dim + d];
-            gs[i] = decay[(n * heads + head) * dim + d];
+        float* ks = sm + b * BUF;
+        float* qs = ks + DR_CHUNK * DP;
+        float* gs = qs + DR_CHUNK * DP;
+        float* vs = gs + DR_CHUNK * DP;
+        float* bs = vs + DR_CHUNK * COLS;
+        if (vec) {  // rows and column runs of whole 16-byte pieces
+            int dq = dim >> 2;
+            for (int i = tid; i < cnt * dq; i += DR_THREADS) {
+                int tt = i / dq, d = (i - tt * dq) * 4;
+                size_t n = (size_t)(start + t0 + tt);
+                cp_async16f(ks + tt * DP + d, k + (n * kv_heads + kvh) * dim + d);
+                cp_async16f(qs + tt * DP + d, q + (n * kv_heads + kvh) * dim + d);
+                cp_async16f(gs + tt * DP + d, decay + (n * heads + head) * dim + d);
+            }
+            for (int i = tid; i < cnt * (COLS / 4); i += DR_THREADS) {
+                int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
+                if (c0 + c < vdim) cp_async16f(vs + tt * COLS + c, v + ((size_t)(start + t0 + tt) * heads + head) * vdim + c0 + c);
+            }
+        } else {
+            for (int tt = 0; tt < cnt; ++tt) {
+                size_t n = (size_t)(start + t0 + tt);
+                for (int d = tid; d < dim; d += DR_THREADS) {
+                    cp_async4(ks + tt * DP + d, k + (n * kv_heads + kvh) * dim + d);
+                    cp_async4(qs + tt * DP + d, q + (n * kv_heads + kvh) * dim + d);
+                    cp_async4(gs + tt * DP + d, decay + (n * heads + head) * dim + d);
+                }
+                if (tid < COLS && c0 + tid < vdim) cp_async4(vs + tt * COLS + tid, v + (n * heads + head) * vdim + c0 + tid);
+            }
         }
-        for (int i = tid; i < cnt * cols_per_block; i += DR_THREADS) {
-            int tt = i / cols_per_block, c = i - tt * cols_per_block;
-            size_t n = (size_t)(start + t0 + tt);
-            vs[i] = (c0 + c < vdim) ? v[(n * heads + head) * vdim + c0 + c] : 0.f;
-        }
-        if (tid < cnt) bs[tid] = beta[(size_t)(start + t0 + tid) * heads + head];
-        __syncthreads();
+        if (tid < cnt) cp_async4(bs + tid, beta + (size_t)(start + t0 + tid) * heads + head);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
+    int b = 0;
+    for (int t0 = 0; t0 < len; t0 += DR_CHUNK, b ^= 1) {
+        int cnt = min(DR_CHUNK, len - t0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // this chunk has landed for everyone, and everyone is done with the other buffer
+        if (t0 + DR_CHUNK < len) stage(t0 + DR_CHUNK, b ^ 1);
+        const float* ks = sm + b * BUF + sub;
+        const float* qs = ks + DR_CHUNK * DP;
+        const float* gs = qs + DR_CHUNK * DP;
+        const float* vs = sm + b * BUF + 3 * DR_CHUNK * DP + my_col;
+        const float* bs = sm + b * BUF + 3 * DR_CHUNK * DP + DR_CHUNK * COLS;
         for (int tt = 0; tt < cnt; ++tt) {
-            const float* kt = ks + tt * dim;
-            const float* qt = qs + tt * dim;
-            const float* gt = gs + tt * dim;
-            float dot = 0.f;
+            const float* kt = ks + tt * DP;
+            const float* qt = qs + tt * DP;
+            const float* gt = gs + tt * DP;
+            float kv[R];
+            float d4[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: shorter chains, a fixed order
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                int r = sub + i * tpc;
-                if (r < dim) {
-                    s[i] *= gt[r];
-                    dot = fmaf(s[i], kt[r], dot);
-                }
+                kv[i] = kt[i * TPC];
+                s[i] *= gt[i * TPC];
+                d4[i & 3] = fmaf(s[i], kv[i], d4[i & 3]);
             }
-            for (int o = tpc >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            float u = bs[tt] * (vs[tt * cols_per_block + tid / tpc] - dot);
-            float rd = 0.f;
+            float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+#pragma unroll
+            for (int o = TPC >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            float u = bs[tt] * ((live ? vs[tt * COLS] : 0.f) - dot);
+            float r4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                int r = sub + i * tpc;
-                if (r < dim) {
-                    s[i] = fmaf(kt[r], u, s[i]);
-                    rd = fmaf(s[i], qt[r], rd);
-                }
+                s[i] = fmaf(kv[i], u, s[i]);
+                r4[i & 3] = fmaf(s[i], qt[i * TPC], r4[i & 3]);
             }
-            for (int o = tpc >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
+            float rd = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+#pragma unroll
+            for (int o = TPC >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
             if (live && sub == 0) out[((size_t)(start + t0 + tt) * heads + head) * vdim + col] = rd;
         }
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            int r = sub + i * tpc;
+            int r = sub + i * TPC;
             if (r < dim) S[r] = s[i];
         }
     }
@@ -220,9 +276,9 @@ IE_API int ie_delta_prep(const float* qkvb, int ld, const float* a, const float*
                          int dim, int vdim, int taps, int num_slots, int* err, void* stream) {
     if (num_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    size_t smem = (size_t)2 * kv_heads * dim * sizeof(float);
+    size_t smem = (size_t)(dim > vdim ? dim : vdim) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    int e = ie_launch(delta_prep_kernel, dim3(num_tokens), dim3(256), smem, s, qkvb, ld, a, conv_w, A_log, dt_bias,
+    int e = ie_launch(delta_prep_kernel, dim3(num_tokens, 2 * kv_heads + 2 * heads + 1), dim3(128), smem, s, qkvb, ld, a, conv_w, A_log, dt_bias,
                       (const float*)state, state_stride, slots, seq_of_token, cu_q, q_out, k_out, v_out, beta,
                       decay, heads, kv_heads, dim, vdim, taps, num_slots, err);
     if (e != 0 || taps < 2) return e;
@@ -231,20 +287,35 @@ IE_API int ie_delta_prep(const float* qkvb, int ld, const float* a, const float*
                      cu_q, (long long)heads * dim * vdim, channels, taps, num_slots);
 }
 
+template <int R, int TPC>
+static int launch_delta_rule(const float* q, const float* k, const float* v, const float* beta, const float* decay,
+                             float* state, long long state_stride, const int* slots, const int* cu_q, float* out,
+                             int num_seqs, int heads, int kv_heads, int dim, int vdim, int num_slots, cudaStream_t s) {
+    constexpr int COLS = DR_THREADS / TPC;
+    size_t smem = (size_t)2 * DR_CHUNK * (3 * R * TPC + COLS + 4) * sizeof(float);
+    static IePerDevice allowed;
+    cudaError_t e = ie_allow_smem(allowed, delta_rule_kernel<R, TPC>, 112 * 1024);  // (dim 512: 99 KB)
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((vdim + COLS - 1) / COLS, heads, num_seqs);
+    return ie_launch(delta_rule_kernel<R, TPC>, grid, dim3(DR_THREADS), smem, s, q, k, v, beta, decay, state,
+                     state_stride, slots, cu_q, out, heads, kv_heads, dim, vdim, num_slots);
+}
+
 IE_API int ie_delta_rule(const float* q, const float* k, const float* v, const float* beta, const float* decay,
                          float* state, long long state_stride, const int* slots, const int* cu_q, float* out,
                          int num_seqs, int heads, int kv_heads, int dim, int vdim, int num_slots, void* stream) {
     if (num_seqs <= 0) return 0;
     constexpr int R = 16;
-    int tpc = 1;
-    while (tpc * R < dim) tpc *= 2;
-    if (tpc > 32) return (int)cudaErrorInvalidValue;  // dim <= 512
-    int cols = DR_THREADS / tpc;
-    dim3 grid((vdim + cols - 1) / cols, heads, num_seqs);
-    size_t smem = ((size_t)DR_CHUNK * (3 * dim + cols) + DR_CHUNK) * sizeof(float);
-    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    return ie_launch(delta_rule_kernel<R>, grid, dim3(DR_THREADS), smem, (cudaStream_t)stream, q, k, v, beta, decay,
-                     state, state_stride, slots, cu_q, out, heads, kv_heads, dim, vdim, tpc, num_slots);
+    cudaStream_t s = (cudaStream_t)stream;
+#define IE_DR_ARGS q, k, v, beta, decay, state, state_stride, slots, cu_q, out, num_seqs, heads, kv_heads, dim, vdim, num_slots, s
+    if (dim <= R) return launch_delta_rule<R, 1>(IE_DR_ARGS);
+    if (dim <= 2 * R) return launch_delta_rule<R, 2>(IE_DR_ARGS);
+    if (dim <= 4 * R) return launch_delta_rule<R, 4>(IE_DR_ARGS);
+    if (dim <= 8 * R) return launch_delta_rule<R, 8>(IE_DR_ARGS);
+    if (dim <= 16 * R) return launch_delta_rule<R, 16>(IE_DR_ARGS);
+    if (dim <= 32 * R) return launch_delta_rule<R, 32>(IE_DR_ARGS);
+#undef IE_DR_ARGS
+    return (int)cudaErrorInvalidValue;  // dim <= 512
 }
 
 IE_API int ie_gated_rms_heads(const float* o, const float* weight, float eps, const float* gate_pre, void* out,

@@ -135,7 +135,26 @@ headwise_linear_kernel(const T* __restrict__ x, long long x_ld, long long x_hs, 
         }
     }
 }
+// out[n, h, :] *= scale[n, h] (bfloat16 rows of `o` entries, rows n * o_ld + h * o_hs apart)
+__global__ void scale_head_rows_kernel(__nv_bfloat16* __restrict__ out, long long o_ld, long long o_hs,
+                                       const float* __restrict__ scale, int heads, int o) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int n = blockIdx.x;
+    for (int i = threadIdx.x; i < heads * o; i += blockDim.x) {
+        int h = i / o, c = i - h * o;
+        __nv_bfloat16* p = out + (size_t)n * o_ld + (size_t)h * o_hs + c;
+        *p = __float2bfloat16_rn(__bfloat162float(*p) * scale[(size_t)n * heads + h]);
+    }
+}
 }  // namespace
+
+IE_API int ie_scale_head_rows(void* out, long long o_ld, long long o_hs, const float* scale, int N, int heads, int o,
+                              void* stream) {
+    if (N <= 0) return 0;
+    return ie_launch(scale_head_rows_kernel, dim3(N), dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, o_ld, o_hs,
+                     scale, heads, o);
+}
 
 IE_API int ie_latent_prep(const float* proj, int ld, const int* positions, const float* table, int rot_dims,
                           int table_rows, const float* norm_w, float eps, void* q_plain, void* q_abs,

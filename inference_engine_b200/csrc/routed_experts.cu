@@ -18,7 +18,7 @@
 
 namespace {
 
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
@@ -36,7 +36,17 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int widt
     for (int e = warp; e < experts; e += ROUTE_THREADS / 32) {
         const float* we = w + (size_t)e * width;
         float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(xs[i], we[i], acc);
+        if (width % 4 == 0) {  // (four partial sums per lane, added in a fixed order)
+            float a4[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i = lane * 4; i < width; i += 128) {
+                float4 wv = *reinterpret_cast<const float4*>(we + i);
+                a4[0] = fmaf(xs[i], wv.x, a4[0]); a4[1] = fmaf(xs[i + 1], wv.y, a4[1]);
+                a4[2] = fmaf(xs[i + 2], wv.z, a4[2]); a4[3] = fmaf(xs[i + 3], wv.w, a4[3]);
+            }
+            acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+        } else {
+            for (int i = lane; i < width; i += 32) acc = fmaf(xs[i], we[i], acc);
+        }
         acc = warp_sum(acc);
         if (lane == 0) score[e] = acc;
     }
@@ -224,24 +234,23 @@ struct TileBF16 {
     }
     __device__ void mma(float* acc) {
         int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        int g = lane >> 2, t = lane & 3;
         int rm = (warp >> 1) * 32, cn = (warp & 1) * 32;
 #pragma unroll
         for (int kk = 0; kk < TILE_K; kk += 16) {
             unsigned a[2][4], b[4][2];
+            // A: a 16 x 16 tile per x4; B: two 8-column tiles (both halves of k) per x4
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi) {
-                int r = rm + mi * 16 + g;
-                a[mi][0] = *reinterpret_cast<const unsigned*>(&as[r][kk + 2 * t]);
-                a[mi][1] = *reinterpret_cast<const unsigned*>(&as[r + 8][kk + 2 * t]);
-                a[mi][2] = *reinterpret_cast<const unsigned*>(&as[r][kk + 2 * t + 8]);
-                a[mi][3] = *reinterpret_cast<const unsigned*>(&as[r + 8][kk + 2 * t + 8]);
+                unsigned addr = (unsigned)__cvta_generic_to_shared(&as[rm + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a[mi][0]), "=r"(a[mi][1]), "=r"(a[mi][2]), "=r"(a[mi][3]) : "r"(addr));
             }
 #pragma unroll
-            for (int ni = 0; ni < 4; ++ni) {
-                int c = cn + ni * 8 + g;
-                b[ni][0] = *reinterpret_cast<const unsigned*>(&bs[c][kk + 2 * t]);
-                b[ni][1] = *reinterpret_cast<const unsigned*>(&bs[c][kk + 2 * t + 8]);
+            for (int nj = 0; nj < 4; nj += 2) {
+                unsigned addr = (unsigned)__cvta_generic_to_shared(
+                    &bs[cn + nj * 8 + (lane & 7) + ((lane >> 4) & 1) * 8][kk + ((lane >> 3) & 1) * 8]);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b[nj][0]), "=r"(b[nj][1]), "=r"(b[nj + 1][0]), "=r"(b[nj + 1][1]) : "r"(addr));
             }
 #pragma unroll
             for (int mi = 0; mi < 2; ++mi)
@@ -376,6 +385,102 @@ routed_down_kernel(const T* __restrict__ y, const T* __restrict__ w, float* __re
         out[((size_t)choice * N + token) * H + n0 + c] = weights[pair] * acc[i];
     }
 }
+
+// ---- bfloat16 with rows that are multiples of 16 bytes: the same tiles fed by cp.async -------------
+// Three stages of (rows of A, NB matrices' rows) in flight; one barrier per 32 columns of k.
+// NB = 2: gate and up, then the activation; NB = 1: the down product, times the routing weight.
+constexpr int PIPE_STAGES = 3;
+constexpr int PIPE_LD = TileBF16::LD;
+constexpr size_t pipe_smem(int nb) { return (size_t)PIPE_STAGES * (1 + nb) * TILE_M * PIPE_LD * sizeof(__nv_bfloat16); }
+
+__device__ __forceinline__ void cp16(void* dst, const void* src, int bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int NB>
+__global__ void __launch_bounds__(128)
+routed_bf16_kernel(const __nv_bfloat16* __restrict__ a_rows, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ out, const float* __restrict__ weights,
+                   const int* __restrict__ sorted, const int* __restrict__ tile_expert, const int* __restrict__ meta,
+                   int top, int N, int K, int F, float limit, int clamp, float alpha, float up_offset) {
+    // NB = 2: a_rows = x [N, K], w = [experts, 2, F, K], output y [pairs, F]
+    // NB = 1: a_rows = y [pairs, K], w = [experts, F, K] (F = the model's width), output out [top, N, F]
+    extern __shared__ __align__(16) unsigned char pipe_raw[];
+    __shared__ const __nv_bfloat16* rows[TILE_M];
+    __shared__ int pair_of[TILE_M];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int tile_id = blockIdx.y;
+    if (tile_id >= meta[0]) return;
+    int e = tile_expert[tile_id], n0 = blockIdx.x * TILE_N;
+    if (threadIdx.x < TILE_M) {
+        int pair = sorted[tile_id * TILE_M + threadIdx.x];
+        pair_of[threadIdx.x] = pair;
+        rows[threadIdx.x] = pair < 0 ? nullptr : a_rows + (size_t)(NB == 2 ? pair / top : pair) * K;
+    }
+    __syncthreads();
+    auto stage_ptr = [&](int stage, int which) {
+        return reinterpret_cast<__nv_bfloat16(*)[PIPE_LD]>(
+            pipe_raw + ((size_t)stage * (1 + NB) + which) * TILE_M * PIPE_LD * sizeof(__nv_bfloat16));
+    };
+    const __nv_bfloat16* wb[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) wb[b] = w + ((size_t)e * NB + b) * F * K;
+    auto issue = [&](int it) {
+        int stage = it % PIPE_STAGES, k0 = it * TILE_K;
+        for (int i = threadIdx.x; i < TILE_M * (TILE_K / 8); i += 128) {
+            int r = i >> 2, k = k0 + (i & 3) * 8;
+            bool in_k = k < K;
+            const __nv_bfloat16* ap = rows[r];
+            cp16(&stage_ptr(stage, 0)[r][(i & 3) * 8], ap != nullptr && in_k ? ap + k : a_rows, ap != nullptr && in_k ? 16 : 0);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                bool ok = in_k && n0 + r < F;
+                cp16(&stage_ptr(stage, 1 + b)[r][(i & 3) * 8], ok ? wb[b] + (size_t)(n0 + r) * K + k : w, ok ? 16 : 0);
+            }
+        }
+    };
+    float acc[NB][32];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[b][i] = 0.f;
+    int iters = (K + TILE_K - 1) / TILE_K;
+    for (int it = 0; it < PIPE_STAGES - 1; ++it) {
+        if (it < iters) issue(it);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    TileBF16 tile;
+    for (int it = 0; it < iters; ++it) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(PIPE_STAGES - 2) : "memory");
+        __syncthreads();
+        if (it + PIPE_STAGES - 1 < iters) issue(it + PIPE_STAGES - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        int stage = it % PIPE_STAGES;
+        tile.as = stage_ptr(stage, 0);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            tile.bs = stage_ptr(stage, 1 + b);
+            tile.mma(acc[b]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        int r, c;
+        TileBF16::where(i, r, c);
+        int pair = pair_of[r];
+        if (pair < 0 || n0 + c >= F) continue;
+        if constexpr (NB == 2) {
+            float g = acc[0][i], u = acc[NB - 1][i];
+            if (clamp) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+            y[(size_t)pair * F + n0 + c] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + up_offset));
+        } else {
+            int token = pair / top, choice = pair - token * top;
+            out[((size_t)choice * N + token) * F + n0 + c] = weights[pair] * acc[0][i];
+        }
+    }
+}
 }  // namespace
 
 IE_API int ie_route_topk(const void* x, int dtype, const float* w, int num_tokens, int width, int experts, int top,
@@ -415,6 +520,10 @@ IE_API int ie_routed_gate_up(const void* x, const void* w, void* y, int dtype, c
     if (max_tiles <= 0) return 0;
     dim3 grid((F + TILE_N - 1) / TILE_N, max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IE_BF16 && K % 8 == 0)
+        return ie_launch(routed_bf16_kernel<2>, grid, dim3(128), pipe_smem(2), s, (const __nv_bfloat16*)x,
+                         (const __nv_bfloat16*)w, (__nv_bfloat16*)y, (float*)nullptr, (const float*)nullptr, sorted,
+                         tile_expert, meta, top, 0, K, F, limit, clamp, alpha, up_offset);
     if (dtype == IE_BF16)
         return ie_launch(routed_gate_up_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                          (const __nv_bfloat16*)w, (__nv_bfloat16*)y, sorted, tile_expert, meta, top, K, F, limit,
@@ -429,6 +538,10 @@ IE_API int ie_routed_down(const void* y, const void* w, float* out, const float*
     if (max_tiles <= 0) return 0;
     dim3 grid((H + TILE_N - 1) / TILE_N, max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IE_BF16 && F % 8 == 0)
+        return ie_launch(routed_bf16_kernel<1>, grid, dim3(128), pipe_smem(1), s, (const __nv_bfloat16*)y,
+                         (const __nv_bfloat16*)w, (__nv_bfloat16*)nullptr, out, weights, sorted, tile_expert, meta,
+                         top, N, F, H, 0.f, 0, 0.f, 0.f);
     if (dtype == IE_BF16)
         return ie_launch(routed_down_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (const __nv_bfloat16*)y,
                          (const __nv_bfloat16*)w, out, weights, sorted, tile_expert, meta, top, N, F, H);

@@ -152,18 +152,19 @@ def build_attention(head_dim: int) -> Path:
 
 
 # Kernels only some mixers and feed-forwards need, each a library of its own that is built the
-# first time a model with such a part runs: name -> source.
+# first time a model with such a part runs: name -> sources.
 PART_LIBRARIES = {
-    "latent": "latent_attention.cu",  # the latent attention's input stage and per-head products
-    "delta": "delta_rule.cu",  # the gated delta rule: convolutions, the recurrence, the read-out norm
-    "routed": "routed_experts.cu",  # routing and the grouped products of the routed feed-forward
+    # the latent attention's input stage and per-head products, and its tensor-core attention
+    "latent": ["latent_attention.cu", "latent_attention_mma.cu"],
+    "delta": ["delta_rule.cu"],  # the gated delta rule: convolutions, the recurrence, the read-out norm
+    "routed": ["routed_experts.cu"],  # routing and the grouped products of the routed feed-forward
 }
 
 
 def build_part_library(name: str) -> Path:
     if name not in PART_LIBRARIES:
         raise BuildError(f"no kernel library {name!r}; there are {sorted(PART_LIBRARIES)}")
-    return build_library(f"ie_b200_{name}", [PART_LIBRARIES[name]])
+    return build_library(f"ie_b200_{name}", list(PART_LIBRARIES[name]))
 
 
 def build_all(prune: bool = True) -> list[Path]:

@@ -128,6 +128,7 @@ class CudaOps:
         self._retired_tickets = []
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
+        self.latent_mma = os.environ.get("IE_B200_LATENT_MMA", "1") != "0"  # tensor-core latent attention
         self.prefill_key_splits = os.environ.get("IE_B200_PREFILL_KEY_SPLITS", "1") != "0"
         # up to this many query tiles x heads per SM a block takes two tiles of a request (a late and an early one)
         self.prefill_paired_max = float(os.environ.get("IE_B200_PREFILL_PAIRED_MAX", 4))
@@ -863,6 +864,28 @@ class CudaOps:
         (``v_cache`` may be the key cache itself); ``out`` is ``[N, nh * value_dim]``."""
         if not 0 < value_dim <= 512:
             raise KernelError(f"value rows of {value_dim} entries are not supported (1 to 512)")
+        if (q.dtype == self.torch.bfloat16 and nkv == 1 and window == 0 and v_cache is k_cache
+                and self.latent_mma and self._part_lib("latent").ie_latent_attention_mma_ok(hd, value_dim)):
+            # one shared row per token, values inside the key rows: the tensor-core kernel; a context is
+            # cut into ranges of key tiles while the blocks are few (from the batch and the tables'
+            # width alone, so that a captured launch stays valid)
+            lib = self._part_lib("latent")
+            bounds = getattr(ctx, "bounds", None)
+            longest = bounds[0] if bounds is not None else ctx.max_q_len
+            rows = lib.ie_latent_attention_rows(longest * nh)
+            max_tiles = -(-longest * nh // rows)
+            blocks = max_tiles * ctx.num_seqs
+            table_tokens = block_tables.shape[1] * page_size
+            splits = max(1, min(self.sm_count // blocks, table_tokens // 128, 16))
+            scratch = None
+            if splits > 1:
+                scratch = self._scratch(ctx, "attn.latent_partial", ctx.num_tokens * nh * splits * (value_dim + 2), q.device)
+            self._check(lib.ie_latent_attention_mma(
+                q.data_ptr(), k_cache.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], ctx.cu_q.data_ptr(),
+                ctx.ctx_lens.data_ptr(), out.data_ptr(), self._ptr(scratch), ctx.num_tokens, ctx.num_seqs, max_tiles,
+                rows, nh, hd, value_dim, page_size, k_cache.shape[0], scale, splits, self._err_ptr, self._stream()),
+                "latent_attention_mma")
+            return
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
@@ -876,6 +899,10 @@ class CudaOps:
         "latent": {
             "ie_latent_prep": "P I P P I I P F P P P P I P I I I I I I P P",
             "ie_headwise_linear": "P L L P P L L P I I I I I P",
+            "ie_scale_head_rows": "P L L P I I I P",
+            "ie_latent_attention_mma_ok": "I I",
+            "ie_latent_attention_mma": "P P P I P P P P I I I I I I I I I F I P P",
+            "ie_latent_attention_rows": "I",
         },
         "delta": {
             "ie_delta_prep": "P I P P P P P L P P P P P P P P I I I I I I I I P P",
@@ -925,6 +952,8 @@ class CudaOps:
             gate.data_ptr(), cache.data_ptr(), _dtype_code(q_abs), self._ptr(slot_mapping), proj.shape[0],
             heads, dim, rot_dim, rank, total_slots, self._err_ptr, self._stream()), "latent_prep")
 
+    HEADWISE_LIBRARY_ROWS = 128  # from this many rows on the per-head products go to the library (bfloat16)
+
     @_kind("latent.headwise")
     def headwise_linear(self, x, w, out, row_scale=None) -> None:
         """``out[n, h, :] = w[h] @ x[n, h, :]`` (times ``row_scale[n, h]``): ``x`` ``[N, H, K]`` and
@@ -935,6 +964,15 @@ class CudaOps:
         if (x.stride(2) != 1 or out.stride(2) != 1 or not w.is_contiguous() or w.shape != (heads, o, k)
                 or out.shape != (n, heads, o) or x.dtype != w.dtype or out.dtype != w.dtype):
             raise KernelError("headwise_linear: shapes, strides or dtypes do not fit")
+        if x.dtype == self.torch.bfloat16 and n >= self.HEADWISE_LIBRARY_ROWS and o % 8 == 0 and k % 8 == 0:
+            # many rows: one strided batched product of the library over the heads, written in place
+            # (both views are batches of row-major matrices with a leading dimension), then the factors
+            self.torch.bmm(x.permute(1, 0, 2), w.transpose(1, 2), out=out.permute(1, 0, 2))
+            if row_scale is not None:
+                self._check(self._part_lib("latent").ie_scale_head_rows(
+                    out.data_ptr(), out.stride(0), out.stride(1), row_scale.data_ptr(), n, heads, o,
+                    self._stream()), "scale_head_rows")
+            return
         self._check(self._part_lib("latent").ie_headwise_linear(
             x.data_ptr(), x.stride(0), x.stride(1), w.data_ptr(), out.data_ptr(), out.stride(0), out.stride(1),
             self._ptr(row_scale), _dtype_code(x), n, heads, o, k, self._stream()), "headwise_linear")
@@ -958,8 +996,8 @@ class CudaOps:
     @_kind("delta.rule")
     def delta_rule(self, q, k, v, beta, decay, state, slots, ctx, out, heads, kv_heads, dim, vdim) -> None:
         """The recurrence itself: every request's tokens of this step in order, from and to its slot."""
-        if dim > 256:
-            raise KernelError(f"the delta rule kernel takes key sizes up to 256, not {dim}")
+        if dim > 512:
+            raise KernelError(f"the delta rule kernel takes key sizes up to 512, not {dim}")
         self._check(self._part_lib("delta").ie_delta_rule(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), state.data_ptr(),
             state.stride(0), slots.data_ptr(), ctx.cu_q.data_ptr(), out.data_ptr(), ctx.num_seqs, heads,

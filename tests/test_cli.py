@@ -44,3 +44,14 @@ def test_generate_runs_from_a_folder(tmp_path, capsys):
     captured = capsys.readouterr()
     assert captured.out.split() == [str(t) for t in want]
     assert "tokens/s" in captured.err
+
+
+def test_info_prints_a_rugedra_shape(tmp_path, capsys):
+    from tests import rugedra_configs as R
+
+    (tmp_path / "config.json").write_text(json.dumps(R.with_ranks(R.MIXED)))
+    assert cli.main(["info", "--model", str(tmp_path), "--gpu-mem", "180"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture        Rugedra" in out and "layers / width      4 / 72" in out
+    assert "channel_delta+moe, latent_attention, latent_attention+dense, channel_delta+dense" in out
+    assert "state per request" in out

@@ -194,7 +194,8 @@ def _feed(runner, cache, mixer, x, portions, env, rid="a"):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [R.latent(3, 12, 8, 20, 20, rot_dims=4), R.latent(5, 8, 16, 8, 24, base=500.0),
-                                   R.latent(1, 64, 32, 48, 96), R.latent(2, 16, 8, 16, 32, rot_dims=0)])
+                                   R.latent(1, 64, 32, 48, 96), R.latent(2, 16, 8, 16, 32, rot_dims=0),
+                                   R.latent(16, 32, 16, 24, 128), R.latent(20, 16, 8, 16, 40)])
 def test_latent_attention_mixer(dtype, sizes):
     width = 72
     env = _env(width, dtype)
@@ -285,7 +286,7 @@ def test_latent_rows_far_away_and_at_page_borders(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [R.delta(6, 2, 12, 20, 4), R.delta(2, 2, 40, 8, 2), R.delta(1, 1, 24, 24, 1),
-                                   R.delta(4, 1, 64, 100, 3), R.delta(2, 1, 200, 16, 3)])
+                                   R.delta(4, 1, 64, 100, 3), R.delta(2, 1, 200, 16, 3), R.delta(1, 1, 300, 8, 2)])
 def test_delta_rule_mixer(dtype, sizes):
     width = 56
     env = _env(width, dtype)
