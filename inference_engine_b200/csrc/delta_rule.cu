@@ -29,19 +29,16 @@ __device__ __forceinline__ float softplus_f(float y) { return y > 20.0f ? y : lo
 // norm over `dim` channels each), the v heads (convolution and silu over `vdim` channels each), the
 // heads' decays (`dim` values each), and one unit for the betas.  channels = 2 * kv_heads * dim +
 // heads * vdim; qkvb rows hold the channels and then `heads` betas.
-__global__ void __launch_bounds__(128)
-delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restrict__ a,
+__device__ __forceinline__ void
+delta_prep_unit(int n, int unit, float* y, float* red,
+                const float* __restrict__ qkvb, int ld, const float* __restrict__ a,
                   const float* __restrict__ conv_w, const float* __restrict__ A_log,
                   const float* __restrict__ dt_bias, const float* __restrict__ state, long long state_stride,
                   const int* __restrict__ slots, const int* __restrict__ seq_of_token,
                   const int* __restrict__ cu_q, float* __restrict__ q_out, float* __restrict__ k_out,
                   float* __restrict__ v_out, float* __restrict__ beta, float* __restrict__ decay,
                   int heads, int kv_heads, int dim, int vdim, int taps, int num_slots, int* err) {
-    extern __shared__ float y[];  // [max(dim, vdim)]: one unit's channels after the convolution
-    __shared__ float red[4];
-    ie_pdl_trigger();
-    ie_pdl_wait();
-    int n = blockIdx.x, unit = blockIdx.y, tid = threadIdx.x;
+    int tid = threadIdx.x;
     int qk = kv_heads * dim, channels = 2 * qk + heads * vdim;
     if (unit == 2 * kv_heads + 2 * heads) {  // the betas
         for (int h = tid; h < heads; h += blockDim.x) beta[(size_t)n * heads + h] = sigmoid_f(qkvb[(size_t)n * ld + channels + h]);
@@ -90,6 +87,28 @@ delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restric
     if (is_q) f *= 1.0f / sqrtf((float)dim);
     float* dst = (is_q ? q_out : k_out) + (size_t)n * qk + (is_q ? unit : unit - kv_heads) * dim;
     for (int i = tid; i < dim; i += blockDim.x) dst[i] = y[i] * f;
+    __syncthreads();  // (y and red are used again by the block's next unit)
+}
+
+// grid: (tokens, blocks per token); a block takes the token's units blockIdx.y, blockIdx.y + gridDim.y, ...
+// (a block per unit when the step has few tokens, a few blocks per token when it has many).
+__global__ void __launch_bounds__(128)
+delta_prep_kernel(const float* __restrict__ qkvb, int ld, const float* __restrict__ a,
+                  const float* __restrict__ conv_w, const float* __restrict__ A_log,
+                  const float* __restrict__ dt_bias, const float* __restrict__ state, long long state_stride,
+                  const int* __restrict__ slots, const int* __restrict__ seq_of_token,
+                  const int* __restrict__ cu_q, float* __restrict__ q_out, float* __restrict__ k_out,
+                  float* __restrict__ v_out, float* __restrict__ beta, float* __restrict__ decay,
+                  int heads, int kv_heads, int dim, int vdim, int taps, int num_slots, int* err) {
+    extern __shared__ float y[];  // [max(dim, vdim)]: one unit's channels after the convolution
+    __shared__ float red[4];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int units = 2 * kv_heads + 2 * heads + 1;
+    for (int unit = blockIdx.y; unit < units; unit += gridDim.y)
+        delta_prep_unit(blockIdx.x, unit, y, red, qkvb, ld, a, conv_w, A_log, dt_bias, state, state_stride, slots,
+                        seq_of_token, cu_q, q_out, k_out, v_out, beta, decay, heads, kv_heads, dim, vdim, taps,
+                        num_slots, err);
 }
 
 // One block per request of the step: the kept inputs become the last taps - 1 of (kept, new).
@@ -278,7 +297,9 @@ IE_API int ie_delta_prep(const float* qkvb, int ld, const float* a, const float*
     cudaStream_t s = (cudaStream_t)stream;
     size_t smem = (size_t)(dim > vdim ? dim : vdim) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    int e = ie_launch(delta_prep_kernel, dim3(num_tokens, 2 * kv_heads + 2 * heads + 1), dim3(128), smem, s, qkvb, ld, a, conv_w, A_log, dt_bias,
+    int units = 2 * kv_heads + 2 * heads + 1;
+    int per_token = num_tokens >= 512 ? (units < 4 ? units : 4) : units;
+    int e = ie_launch(delta_prep_kernel, dim3(num_tokens, per_token), dim3(128), smem, s, qkvb, ld, a, conv_w, A_log, dt_bias,
                       (const float*)state, state_stride, slots, seq_of_token, cu_q, q_out, k_out, v_out, beta,
                       decay, heads, kv_heads, dim, vdim, taps, num_slots, err);
     if (e != 0 || taps < 2) return e;

@@ -72,7 +72,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     static_assert(LM_WARPS % N_TILES == 0 && MT % WPN == 0 && MPW >= 1 && KPT % 4 == 0 && TPR <= 32, "shape");
     ie_pdl_trigger();
     ie_pdl_wait();
-    int seq = blockIdx.y, tile = blockIdx.x, split = blockIdx.z;
+    // (the blocks of a request's last rows see the most keys: they start first)
+    int seq = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x, split = blockIdx.z;
     int q0 = cu_q[seq], q_len = cu_q[seq + 1] - q0;
     int rows_total = q_len * heads;
     int row0 = tile * LM_ROWS;
@@ -167,16 +168,20 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                 unsigned b[4];
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(kb + kk * 2));
+                // (all fragments of the 32 columns first, then the products: a load's latency is paid
+                // once per 32 columns, not once per product)
+                unsigned a[MPW][2][4];
 #pragma unroll
-                for (int i = 0; i < MPW; ++i) {
-                    unsigned a[4];
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(qa + (i * 16 * ld + kk) * 2));
-                    mma_bf16(c[i], a, b);
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(qa + (i * 16 * ld + kk + 16) * 2));
-                    mma_bf16(c[i], a, b + 2);
-                }
+                for (int i = 0; i < MPW; ++i)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(a[i][h][0]), "=r"(a[i][h][1]), "=r"(a[i][h][2]), "=r"(a[i][h][3])
+                                     : "r"(qa + (i * 16 * ld + kk + h * 16) * 2));
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < MPW; ++i) mma_bf16(c[i], a[i][h], b + 2 * h);
             }
             if (kk < dkp) {  // a last step of 16
                 unsigned b[2];
@@ -263,15 +268,17 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                 for (int mt = 0; mt < MT; ++mt) {
                     if (moved) { acc[mt][i][0] *= a0[mt]; acc[mt][i][1] *= a0[mt]; acc[mt][i][2] *= a1[mt]; acc[mt][i][3] *= a1[mt]; }
                 }
+                unsigned b[LM_KEYS / 16][2];
 #pragma unroll
                 for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
-                    unsigned b[2];
                     unsigned addr = (unsigned)__cvta_generic_to_shared(ks + (kk * 16 + (lane & 15)) * ld + nt * 8);
                     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                                 : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) mma_bf16(acc[mt][i], pa[mt][kk], b);
+                                 : "=r"(b[kk][0]), "=r"(b[kk][1]) : "r"(addr));
                 }
+#pragma unroll
+                for (int kk = 0; kk < LM_KEYS / 16; ++kk)
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) mma_bf16(acc[mt][i], pa[mt][kk], b[kk]);
             }
         }
     }
