@@ -11,7 +11,7 @@
 //  * delta_conv_tail: the slot's kept inputs moved on by the step's tokens.
 //  * delta_rule: per token, in order:  S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;
 //    o = S^T q.  Columns of S do not interact: a block owns some columns of one head of one
-//    request, a group of TPC lanes one column (lane j of the group holds rows j, j + TPC, ...),
+//    request, a group of TPC lanes one column (lane j of the group holds rows R j .. R j + R - 1),
 //    and walks the request's tokens of this step in order, eight at a time through shared memory.
 //    Each sum over rows is taken in an order that depends on `dim` alone.
 //  * gated_rms_heads: o / rms(o) per head, times a weight, times sigmoid(gate).
@@ -149,8 +149,10 @@ __device__ __forceinline__ void cp_async16f(float* dst, const float* src) {
 
 // grid: (column blocks, heads, requests).  R rows per lane; TPC lanes per column (a power of two).
 // The tokens' k, q, decay, v and beta come through shared memory eight tokens at a time, the next
-// eight on their way (cp.async, two buffers) while these are worked on.  Rows are padded to
-// R * TPC entries that read as zero, so the inner loops carry no bounds checks.
+// eight on their way (cp.async, two buffers) while these are worked on.  A lane holds R (8 or 16)
+// consecutive rows of its column; in shared memory a token's k, q and decay lie in groups of R
+// entries R + 4 floats apart, so that a lane fetches its rows with 16-byte loads and the lanes of a
+// column hit different banks; entries beyond `dim` read as zero, so the inner loops carry no bounds checks.
 template <int R, int TPC>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
@@ -158,7 +160,9 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   long long state_stride, const int* __restrict__ slots, const int* __restrict__ cu_q,
                   float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int num_slots) {
     extern __shared__ __align__(16) float sm[];  // two buffers of: k, q, g [CHUNK][DP] each, v [CHUNK][COLS], beta [CHUNK]
-    constexpr int COLS = DR_THREADS / TPC, DP = R * TPC;
+    static_assert(R == 8 || R == 16, "a lane's rows are one group of 8 or 16");
+    constexpr int GS = R + 4;  // a lane's group of R entries, and four floats to the next lane's
+    constexpr int COLS = DR_THREADS / TPC, DP = GS * TPC;  // a token's row of k (q, decay)
     constexpr int BUF = DR_CHUNK * (3 * DP + COLS + 4);
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -174,15 +178,12 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        int r = sub + i * TPC;
+        int r = sub * R + i;
         s[i] = (live && r < dim) ? S[r] : 0.f;
     }
-    if (DP > dim)  // the rows' padding: k and q read as zero there (the copies never touch it)
-        for (int i = tid; i < 2 * DR_CHUNK * 3 * (DP - dim); i += DR_THREADS) {
-            int row = i / (DP - dim), c = dim + i % (DP - dim);  // row: (buffer, array, token)
-            int b = row / (3 * DR_CHUNK), rest = row % (3 * DR_CHUNK);
-            sm[b * BUF + rest * DP + c] = 0.f;
-        }
+    // what the copies never touch (entries beyond dim, the gaps) reads as zero
+    for (int i = tid; i < 2 * BUF; i += DR_THREADS) sm[i] = 0.f;
+    __syncthreads();
     int c0 = blockIdx.x * COLS;
     bool vec = (dim % 4 == 0) && (vdim % 4 == 0) && (COLS % 4 == 0);
     auto stage = [&](int t0, int b) {  // the chunk's values on their way into buffer b
@@ -197,9 +198,10 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             for (int i = tid; i < cnt * dq; i += DR_THREADS) {
                 int tt = i / dq, d = (i - tt * dq) * 4;
                 size_t n = (size_t)(start + t0 + tt);
-                cp_async16f(ks + tt * DP + d, k + (n * kv_heads + kvh) * dim + d);
-                cp_async16f(qs + tt * DP + d, q + (n * kv_heads + kvh) * dim + d);
-                cp_async16f(gs + tt * DP + d, decay + (n * heads + head) * dim + d);
+                int at = tt * DP + (d / R) * GS + (d % R);
+                cp_async16f(ks + at, k + (n * kv_heads + kvh) * dim + d);
+                cp_async16f(qs + at, q + (n * kv_heads + kvh) * dim + d);
+                cp_async16f(gs + at, decay + (n * heads + head) * dim + d);
             }
             for (int i = tid; i < cnt * (COLS / 4); i += DR_THREADS) {
                 int tt = i / (COLS / 4), c = (i % (COLS / 4)) * 4;
@@ -209,9 +211,10 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             for (int tt = 0; tt < cnt; ++tt) {
                 size_t n = (size_t)(start + t0 + tt);
                 for (int d = tid; d < dim; d += DR_THREADS) {
-                    cp_async4(ks + tt * DP + d, k + (n * kv_heads + kvh) * dim + d);
-                    cp_async4(qs + tt * DP + d, q + (n * kv_heads + kvh) * dim + d);
-                    cp_async4(gs + tt * DP + d, decay + (n * heads + head) * dim + d);
+                    int at = tt * DP + (d / R) * GS + (d % R);
+                    cp_async4(ks + at, k + (n * kv_heads + kvh) * dim + d);
+                    cp_async4(qs + at, q + (n * kv_heads + kvh) * dim + d);
+                    cp_async4(gs + at, decay + (n * heads + head) * dim + d);
                 }
                 if (tid < COLS && c0 + tid < vdim) cp_async4(vs + tt * COLS + tid, v + (n * heads + head) * vdim + c0 + tid);
             }
@@ -226,7 +229,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();  // this chunk has landed for everyone, and everyone is done with the other buffer
         if (t0 + DR_CHUNK < len) stage(t0 + DR_CHUNK, b ^ 1);
-        const float* ks = sm + b * BUF + sub;
+        const float* ks = sm + b * BUF + sub * GS;
         const float* qs = ks + DR_CHUNK * DP;
         const float* gs = qs + DR_CHUNK * DP;
         const float* vs = sm + b * BUF + 3 * DR_CHUNK * DP + my_col;
@@ -235,12 +238,17 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             const float* kt = ks + tt * DP;
             const float* qt = qs + tt * DP;
             const float* gt = gs + tt * DP;
-            float kv[R];
+            float kv[R], gv[R], qv[R];
+#pragma unroll
+            for (int j = 0; j < R / 4; ++j) {
+                *reinterpret_cast<float4*>(kv + 4 * j) = reinterpret_cast<const float4*>(kt)[j];
+                *reinterpret_cast<float4*>(gv + 4 * j) = reinterpret_cast<const float4*>(gt)[j];
+                *reinterpret_cast<float4*>(qv + 4 * j) = reinterpret_cast<const float4*>(qt)[j];
+            }
             float d4[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: shorter chains, a fixed order
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                kv[i] = kt[i * TPC];
-                s[i] *= gt[i * TPC];
+                s[i] *= gv[i];
                 d4[i & 3] = fmaf(s[i], kv[i], d4[i & 3]);
             }
             float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
@@ -251,7 +259,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
             for (int i = 0; i < R; ++i) {
                 s[i] = fmaf(kv[i], u, s[i]);
-                r4[i & 3] = fmaf(s[i], qt[i * TPC], r4[i & 3]);
+                r4[i & 3] = fmaf(s[i], qv[i], r4[i & 3]);
             }
             float rd = (r4[0] + r4[1]) + (r4[2] + r4[3]);
 #pragma unroll
@@ -262,7 +270,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     if (live) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            int r = sub + i * TPC;
+            int r = sub * R + i;
             if (r < dim) S[r] = s[i];
         }
     }
@@ -313,9 +321,9 @@ static int launch_delta_rule(const float* q, const float* k, const float* v, con
                              float* state, long long state_stride, const int* slots, const int* cu_q, float* out,
                              int num_seqs, int heads, int kv_heads, int dim, int vdim, int num_slots, cudaStream_t s) {
     constexpr int COLS = DR_THREADS / TPC;
-    size_t smem = (size_t)2 * DR_CHUNK * (3 * R * TPC + COLS + 4) * sizeof(float);
+    size_t smem = (size_t)2 * DR_CHUNK * (3 * (R + 4) * TPC + COLS + 4) * sizeof(float);
     static IePerDevice allowed;
-    cudaError_t e = ie_allow_smem(allowed, delta_rule_kernel<R, TPC>, 112 * 1024);  // (dim 512: 99 KB)
+    cudaError_t e = ie_allow_smem(allowed, delta_rule_kernel<R, TPC>, 160 * 1024);  // (dim 512: 124 KB)
     if (e != cudaSuccess) return (int)e;
     dim3 grid((vdim + COLS - 1) / COLS, heads, num_seqs);
     return ie_launch(delta_rule_kernel<R, TPC>, grid, dim3(DR_THREADS), smem, s, q, k, v, beta, decay, state,
@@ -326,15 +334,18 @@ IE_API int ie_delta_rule(const float* q, const float* k, const float* v, const f
                          float* state, long long state_stride, const int* slots, const int* cu_q, float* out,
                          int num_seqs, int heads, int kv_heads, int dim, int vdim, int num_slots, void* stream) {
     if (num_seqs <= 0) return 0;
-    constexpr int R = 16;
     cudaStream_t s = (cudaStream_t)stream;
 #define IE_DR_ARGS q, k, v, beta, decay, state, state_stride, slots, cu_q, out, num_seqs, heads, kv_heads, dim, vdim, num_slots, s
-    if (dim <= R) return launch_delta_rule<R, 1>(IE_DR_ARGS);
-    if (dim <= 2 * R) return launch_delta_rule<R, 2>(IE_DR_ARGS);
-    if (dim <= 4 * R) return launch_delta_rule<R, 4>(IE_DR_ARGS);
-    if (dim <= 8 * R) return launch_delta_rule<R, 8>(IE_DR_ARGS);
-    if (dim <= 16 * R) return launch_delta_rule<R, 16>(IE_DR_ARGS);
-    if (dim <= 32 * R) return launch_delta_rule<R, 32>(IE_DR_ARGS);
+    // Eight rows per lane for small key sizes (2,048 tokens of 8 heads of 64 x 64: 0.54 ms against 0.65 with
+    // sixteen), sixteen from there on (16 heads of 128 x 128: 0.64 ms against 0.75 with eight: the exchange
+    // between a column's lanes has a step more).
+    if (dim <= 8) return launch_delta_rule<8, 1>(IE_DR_ARGS);
+    if (dim <= 16) return launch_delta_rule<8, 2>(IE_DR_ARGS);
+    if (dim <= 32) return launch_delta_rule<8, 4>(IE_DR_ARGS);
+    if (dim <= 64) return launch_delta_rule<8, 8>(IE_DR_ARGS);
+    if (dim <= 128) return launch_delta_rule<16, 8>(IE_DR_ARGS);
+    if (dim <= 256) return launch_delta_rule<16, 16>(IE_DR_ARGS);
+    if (dim <= 512) return launch_delta_rule<16, 32>(IE_DR_ARGS);
 #undef IE_DR_ARGS
     return (int)cudaErrorInvalidValue;  // dim <= 512
 }

@@ -51,7 +51,13 @@ DELTA_ONLY = config(48, 61, [
     ("channel_delta", delta(4, 4, 8, 12, 3), None),
 ], mult=0.5)
 
-CONFIGS = {"mixed": MIXED, "latent_only": LATENT_ONLY, "delta_only": DELTA_ONLY}
+# nothing a multiple of 4: widths, rows, sizes of heads, experts
+ODD = config(50, 53, [
+    ("latent_attention", latent(3, 10, 6, 14, 18, rot_dims=2), moe(12, 3, 2, 1, 1)),
+    ("channel_delta", delta(3, 1, 10, 14, 2), dense(30)),
+], max_positions=200)
+
+CONFIGS = {"mixed": MIXED, "latent_only": LATENT_ONLY, "delta_only": DELTA_ONLY, "odd": ODD}
 RANKS = {"decay_rank": 6, "gate_rank": 10}
 
 
