@@ -1,1 +1,1 @@
-from . import llama, rugedra  # noqa: F401 (register LlamaForCausalLM and Rugedra)
+from . import llama, ravapel, rugedra  # noqa: F401 (register LlamaForCausalLM, Ravapel and Rugedra)

@@ -4,8 +4,9 @@ per-request state of fixed size.  No torch; device memory is in ``cache/storage.
 A *cache group* is a set of layers with the same needs (same key/value heads and head size,
 and either all positions or a window of the latest ones).  Each paged group has pages and a
 page pool of its own and one block table per request: entry ``i`` is the page that holds
-positions ``[i * page_size, (i + 1) * page_size)``, or ``-1`` once a window has passed it
-and the page was given back.  Token ``p`` lives in flat slot
+positions ``[i * page_size, (i + 1) * page_size)``, or ``-1`` once a window (or, in a group
+whose queries see their own chunk of positions only, the start of the current chunk) has passed
+it and the page was given back.  Token ``p`` lives in flat slot
 ``table[p // page_size] * page_size + p % page_size`` (engine/runtime/block_manager.py:171-174).
 
 Pages are taken when a request grows (``grow``), given back when it ends (``free``) or
@@ -30,6 +31,7 @@ class PagedGroupSpec:
     head_dim: int
     window: int | None = None  # None: every position stays; else the latest ``window`` do
     value_dim: int | None = None  # size of a value row: None = head_dim; 0 = no value rows are kept
+    chunk: int | None = None  # queries see their own chunk of this many positions only (None: no chunks)
 
     @property
     def values_per_token(self) -> int:
@@ -68,7 +70,7 @@ class CacheManager:
         if len(counts) != len(self.paged_groups):
             raise ValueError("num_pages needs one entry per paged cache group")
         self.pools = [PagePool(n) for n in counts]
-        self._has_window = any(g.window is not None for g in self.paged_groups)
+        self._has_window = any(g.window is not None or g.chunk is not None for g in self.paged_groups)
         self.slots = SlotPool(max_requests)
         self._requests: dict[object, _Request] = {}
         # A dense copy of the block tables, one row per state slot (the last row is the
@@ -120,10 +122,13 @@ class CacheManager:
         return self._requests[req_id].tables[group]
 
     def _first_needed_page(self, group: int, first_query_pos: int) -> int:
-        window = self.paged_groups[group].window
-        if window is None:
-            return 0
-        return max(first_query_pos - window + 1, 0) // self.page_size
+        spec = self.paged_groups[group]
+        first = 0
+        if spec.window is not None:
+            first = max(first_query_pos - spec.window + 1, 0)
+        if spec.chunk is not None:  # (the chunk of the next query starts at a multiple of its size)
+            first = max(first, first_query_pos // spec.chunk * spec.chunk)
+        return first // self.page_size
 
     def pages_needed(self, req_id, num_computed: int, num_tokens: int) -> list[int]:
         """Extra pages per group so that positions up to ``num_tokens`` are held, given
@@ -194,7 +199,8 @@ class CacheManager:
         last_page = -(-num_tokens // self.page_size)
         simple = True
         for g, table in enumerate(req.tables):
-            if self.paged_groups[g].window is not None or len(table) < last_page:
+            if (self.paged_groups[g].window is not None or self.paged_groups[g].chunk is not None
+                    or len(table) < last_page):
                 simple = False
                 break
         if simple:

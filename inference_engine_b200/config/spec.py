@@ -46,6 +46,9 @@ class ScheduleEntry:
 
     layer: int
     cache_from: int | None = None
+    # Name of a stream part (``ModelSpec.stream_parts``) that rewrites the residual stream right
+    # before this run of the layer (after everything the earlier runs added).
+    before: str | None = None
 
 
 @dataclass(frozen=True)
@@ -62,6 +65,7 @@ class ModelSpec:
     head: PartSpec
     eos_token_ids: tuple[int, ...] = ()
     bos_token_id: int | None = None
+    stream_parts: dict[str, PartSpec] = field(default_factory=dict)
 
     def validate(self) -> None:
         if not self.layers:
@@ -71,6 +75,9 @@ class ModelSpec:
         for i, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"run order names layer {entry.layer}, which does not exist")
+            if entry.before is not None and entry.before not in self.stream_parts:
+                raise ValueError(f"entry {i} of the run order names the stream part {entry.before!r}, "
+                                 "which the model does not have")
             if entry.cache_from is not None:
                 if not 0 <= entry.cache_from < i:
                     raise ValueError(

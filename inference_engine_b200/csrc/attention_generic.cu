@@ -14,6 +14,9 @@
 // A value row may be shorter than a key row and may live inside it: `hdv` entries at the start of
 // rows `v_stride` apart (a mixer that caches one shared latent row per token passes the key cache
 // as the value cache too, `v_stride` = the key row and `hdv` = the latent's size).
+// `chunk` > 0: a query sees only the keys of its own chunk of that many positions (counted from the
+// request's position 0).  `head_bias` != null: the weight of a visible key is sigmoid(score +
+// head_bias[head]) and the weights are not normalised over the keys (no softmax).
 #include "common.cuh"
 #include <math.h>
 
@@ -58,7 +61,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int table_width, const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, T* __restrict__ out,
                                int nh, int nkv, int hd, int hdv, int v_stride, int page_size, int total_pages,
-                               float scale, int window, int* err) {
+                               float scale, int window, int chunk, const float* __restrict__ head_bias,
+                               int* err) {
     extern __shared__ float q_smem[];  // [WARPS][hd]
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -75,6 +79,9 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
     __syncwarp();
 
     int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);  // chunks are counted from the request's position 0
+    const bool gated = head_bias != nullptr;  // sigmoid(score + bias) per key, not normalised over keys
+    float hb = gated ? head_bias[head] : 0.f;
     float m = -INFINITY, l = 0.f;
     float acc[MAX_ACC];
 #pragma unroll
@@ -96,12 +103,17 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                 s = (hd % 8 == 0 ? dot_row(qs, k_cache + row * hd, hd) : dot_row_any(qs, k_cache + row * hd, hd)) * scale;
             }
         }
-        float m_new = fmaxf(m, warp_max(s));
-        float p = valid ? expf(s - m_new) : 0.f;
-        float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
-        l = l * alpha + warp_sum(p);
+        float m_new = m, p;
+        if (gated) {
+            p = valid ? 1.0f / (1.0f + expf(-(s + hb))) : 0.f;
+        } else {
+            m_new = fmaxf(m, warp_max(s));
+            p = valid ? expf(s - m_new) : 0.f;
+            float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
+            l = l * alpha + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < MAX_ACC; ++i) acc[i] *= alpha;
+            for (int i = 0; i < MAX_ACC; ++i) acc[i] *= alpha;
+        }
         int count = min(32, pos - t0 + 1);
         for (int j = 0; j < count; ++j) {
             float pj = __shfl_sync(0xffffffffu, p, j);
@@ -117,7 +129,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         m = m_new;
     }
     T* orow = out + ((size_t)token * nh + head) * hdv;
-    float inv = l > 0.f ? 1.0f / l : 0.f;
+    float inv = gated ? 1.0f : (l > 0.f ? 1.0f / l : 0.f);
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) {
         int d = lane + 32 * i;
@@ -130,8 +142,8 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
                                       int dtype, const int* block_tables, int table_width,
                                       const int* seq_of_token, const int* positions, void* out,
                                       int num_tokens, int nh, int nkv, int hd, int hdv, int v_stride,
-                                      int page_size, int total_pages, float scale, int window, int* err,
-                                      void* stream) {
+                                      int page_size, int total_pages, float scale, int window, int chunk,
+                                      const float* head_bias, int* err, void* stream) {
     if (num_tokens <= 0) return 0;
     if (hd < 1 || hdv < 1 || hdv > 32 * MAX_ACC || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     dim3 grid((nh + WARPS - 1) / WARPS, num_tokens);
@@ -141,11 +153,11 @@ IE_API int ie_paged_attention_generic(const void* q, const void* k_cache, const 
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
             block_tables, table_width, seq_of_token, positions, (__nv_bfloat16*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, err);
     else
         paged_attention_generic_kernel<<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_tables, table_width, seq_of_token, positions, (float*)out,
-            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, err);
+            nh, nkv, hd, hdv, v_stride, page_size, total_pages, scale, window, chunk, head_bias, err);
     return IE_LAUNCH_CHECK();
 }

@@ -1,0 +1,241 @@
+// Operations on the residual stream and around it that models with hashed bigram embeddings,
+// norms on both sides of a sublayer, biased gated feed-forwards and re-injected embeddings need:
+//
+//  * bigram_embedding: out[n] = embed[id] + bigram[row], row = (prev * mul_prev + id * mul_cur) mod
+//    buckets, or row `buckets` for a request's first token.  The token before a step's first one is
+//    kept per request in a state slot (as the integer's bits) and moved on by the same block that
+//    read it.
+//  * sandwich_norm: y = sum of the parts of `delta` (+ bias); y <- rms(y) * post_w (if post_w);
+//    h += y; out = rms(h) * pre_w (if out).  One block per row; both sums of squares are added in
+//    an order that depends on the row's width alone.
+//  * silu_mul_bias: out = silu(g + bg) * (u + bu) from 32-bit rows that hold gates, then ups.
+//  * concat_cast: out[n] = [h[n]; x0[n]] in the compute dtype.
+//  * weighted_sum: out = sa * a + sb * b (32-bit).
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+bigram_embedding_kernel(const T* __restrict__ embed, const T* __restrict__ bigram, const int* __restrict__ ids,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                        const int* __restrict__ cu_q, const int* __restrict__ slots, int* __restrict__ state,
+                        long long state_stride, int num_slots, float* __restrict__ out, int hidden, int vocab,
+                        int buckets, long long mul_prev, long long mul_cur, int* err) {
+    __shared__ int s_row;
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) ie_report(err, IE_ERR_TOKEN_ID, id, n);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)n * hidden + i] = 0.f;
+        return;
+    }
+    if (threadIdx.x == 0) {
+        int seq = seq_of_token[n], first = cu_q[seq], end = cu_q[seq + 1];
+        int slot = slots[seq];
+        bool slot_ok = slot >= 0 && slot < num_slots;
+        int row = buckets;
+        if (positions[n] > 0) {
+            int prev = 0;
+            if (n > first) prev = ids[n - 1];
+            else if (slot_ok) prev = state[(size_t)slot * state_stride];
+            else ie_report(err, IE_ERR_PAGE, slot, n);
+            row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % (long long)buckets);
+            if (row < 0) row += buckets;
+        }
+        // the request's last token of this step is what its next step starts from; the block of the
+        // request's first token is the only one that touches the slot, after it has read it
+        if (n == first && end > first && slot_ok) state[(size_t)slot * state_stride] = ids[end - 1];
+        s_row = row;
+    }
+    __syncthreads();
+    const T* e = embed + (size_t)id * hidden;
+    const T* b = bigram + (size_t)s_row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)n * hidden + i] = ie_load(e + i) + ie_load(b + i);
+}
+
+constexpr int SN_THREADS = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();  // (red may still be read from the sum before)
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < SN_THREADS / 32; ++w) total += red[w];
+    return total;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(SN_THREADS)
+sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
+                     const float* __restrict__ bias, const float* __restrict__ post_w, float post_eps,
+                     const float* __restrict__ pre_w, float pre_eps, OutT* __restrict__ out,
+                     const int* __restrict__ rows, int hidden) {
+    extern __shared__ float row_buf[];  // [hidden]
+    __shared__ float red[SN_THREADS / 32];
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    int r = blockIdx.x;
+    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    if (delta != nullptr) {
+        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
+            float y = delta[src + i];
+            for (int p = 1; p < num_partials; ++p) y += delta[p * partial_stride + src + i];
+            if (bias) y += bias[i];
+            row_buf[i] = y;
+            ss = fmaf(y, y, ss);
+        }
+        float inv = 1.0f;
+        if (post_w != nullptr) inv = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + post_eps);
+        ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
+            float y = row_buf[i];
+            if (post_w != nullptr) y = post_w[i] * (y * inv);
+            float x = h[src + i] + y;
+            row_buf[i] = x;
+            if (rows == nullptr) h[src + i] = x;
+            ss = fmaf(x, x, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
+            float x = h[src + i];
+            row_buf[i] = x;
+            ss = fmaf(x, x, ss);
+        }
+    }
+    if (out == nullptr) return;
+    float inv2 = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + pre_eps);
+    for (int i = threadIdx.x; i < hidden; i += SN_THREADS)
+        ie_store(out + (size_t)r * hidden + i, pre_w[i] * (row_buf[i] * inv2));
+}
+
+template <typename T>
+__global__ void silu_mul_bias_kernel(const float* __restrict__ gate_up, const float* __restrict__ bias,
+                                     T* __restrict__ out, int inter, size_t total) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        size_t row = idx / inter;
+        int i = (int)(idx - row * inter);
+        float g = gate_up[row * 2 * inter + i], u = gate_up[row * 2 * inter + inter + i];
+        if (bias) { g += bias[i]; u += bias[inter + i]; }
+        ie_store(out + idx, g / (1.0f + expf(-g)) * u);
+    }
+}
+
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
+                                   int width, size_t total) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        size_t row = idx / (2 * width);
+        int i = (int)(idx - row * 2 * width);
+        float v = i < width ? a[row * width + i] : b[row * width + (i - width)];
+        ie_store(out + idx, v);
+    }
+}
+
+__global__ void weighted_sum_kernel(const float* __restrict__ a, float sa, const float* __restrict__ b, float sb,
+                                    float* __restrict__ out, size_t total) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) out[idx] = fmaf(sb, b[idx], sa * a[idx]);
+}
+
+inline int grid_for(size_t total, int threads) {
+    size_t want = (total + threads - 1) / threads;
+    return (int)(want < 148 * 16 ? want : 148 * 16);
+}
+}  // namespace
+
+IE_API int ie_bigram_embedding(const void* embed, const void* bigram, int table_dtype, const int* ids,
+                               const int* positions, const int* seq_of_token, const int* cu_q, const int* slots,
+                               void* state, long long state_stride, int num_slots, float* out, int num_tokens,
+                               int hidden, int vocab, int buckets, long long mul_prev, long long mul_cur, int* err,
+                               void* stream) {
+    if (num_tokens <= 0) return 0;
+    if (buckets < 1) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_dtype == IE_BF16)
+        return ie_launch(bigram_embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, s,
+                         (const __nv_bfloat16*)embed, (const __nv_bfloat16*)bigram, ids, positions, seq_of_token, cu_q,
+                         slots, (int*)state, state_stride, num_slots, out, hidden, vocab, buckets, mul_prev, mul_cur, err);
+    return ie_launch(bigram_embedding_kernel<float>, dim3(num_tokens), dim3(128), 0, s, (const float*)embed,
+                     (const float*)bigram, ids, positions, seq_of_token, cu_q, slots, (int*)state, state_stride,
+                     num_slots, out, hidden, vocab, buckets, mul_prev, mul_cur, err);
+}
+
+// `out` may be null (only the residual stream is brought up to date); `delta` may be null (a plain
+// norm of h); `rows` selects rows, and then h is not modified.
+IE_API int ie_sandwich_norm(float* h, const float* delta, int num_partials, long long partial_stride,
+                            const float* bias, const float* post_w, float post_eps, const float* pre_w,
+                            float pre_eps, void* out, int out_dtype, const int* rows, int num_rows, int hidden,
+                            void* stream) {
+    if (num_rows <= 0) return 0;
+    if (delta != nullptr && num_partials < 1) return (int)cudaErrorInvalidValue;
+    if (out != nullptr && pre_w == nullptr) return (int)cudaErrorInvalidValue;
+    size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16) {
+        static IePerDevice allowed;
+        if (smem > 48 * 1024) {
+            cudaError_t e = ie_allow_smem(allowed, sandwich_norm_kernel<__nv_bfloat16>, 200 * 1024);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return ie_launch(sandwich_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,
+                         num_partials, (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps,
+                         (__nv_bfloat16*)out, rows, hidden);
+    }
+    static IePerDevice allowed32;
+    if (smem > 48 * 1024) {
+        cudaError_t e = ie_allow_smem(allowed32, sandwich_norm_kernel<float>, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return ie_launch(sandwich_norm_kernel<float>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta, num_partials,
+                     (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps, (float*)out, rows, hidden);
+}
+
+IE_API int ie_silu_mul_bias(const float* gate_up, const float* bias, void* out, int out_dtype, int num_rows,
+                            int inter, void* stream) {
+    size_t total = (size_t)num_rows * inter;
+    if (total == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16)
+        return ie_launch(silu_mul_bias_kernel<__nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0, s, gate_up,
+                         bias, (__nv_bfloat16*)out, inter, total);
+    return ie_launch(silu_mul_bias_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, s, gate_up, bias,
+                     (float*)out, inter, total);
+}
+
+IE_API int ie_concat_cast(const float* a, const float* b, void* out, int out_dtype, int num_rows, int width,
+                          void* stream) {
+    size_t total = (size_t)num_rows * 2 * width;
+    if (total == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16)
+        return ie_launch(concat_cast_kernel<__nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0, s, a, b,
+                         (__nv_bfloat16*)out, width, total);
+    return ie_launch(concat_cast_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, s, a, b, (float*)out, width,
+                     total);
+}
+
+IE_API int ie_weighted_sum(const float* a, float sa, const float* b, float sb, float* out, long long total,
+                           void* stream) {
+    if (total <= 0) return 0;
+    return ie_launch(weighted_sum_kernel, dim3(grid_for((size_t)total, 256)), dim3(256), 0, (cudaStream_t)stream, a,
+                     sa, b, sb, out, (size_t)total);
+}

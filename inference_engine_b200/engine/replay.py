@@ -20,7 +20,7 @@ from .batch import StepEntry
 from .loading import load_model
 from .runner import make_runner
 
-LIVE_REQUESTS = 8  # state slots; a trace keeps at most four requests alive
+LIVE_REQUESTS = 4  # state slots: a trace keeps at most four requests alive, so slots are used again
 
 
 class ReplaySession:

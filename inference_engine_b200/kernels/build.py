@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-r
 
 # Sources of the always-needed library.  Kernels specialised on a model's sizes are listed
 # in SPECIALISED and built by `build_specialised` with -D flags.
-CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_tma.cu", "gemm_tc5.cu", "attention_generic.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "stream_ops.cu", "gemm_f32.cu", "gemm_tma.cu", "gemm_tc5.cu", "attention_generic.cu", "sampling.cu"]
 
 
 class BuildError(RuntimeError):
@@ -158,6 +158,11 @@ PART_LIBRARIES = {
     "latent": ["latent_attention.cu", "latent_attention_mma.cu"],
     "delta": ["delta_rule.cu"],  # the gated delta rule: convolutions, the recurrence, the read-out norm
     "routed": ["routed_experts.cu"],  # routing and the grouped products of the routed feed-forward
+    # recurrent mixers with a decaying matrix state (gated-write linear attention, exponential-gate
+    # matrix memory): input convolution, gates, the recurrence, the read-out
+    "recurrent": ["gated_recurrence.cu"],
+    # attention with normalised queries and keys and sigmoid weights: the input stage
+    "gated_attn": ["gated_attention.cu"],
 }
 
 

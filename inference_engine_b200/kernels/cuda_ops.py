@@ -210,8 +210,13 @@ class CudaOps:
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_ok": [I, I, I],
-            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
+            "ie_bigram_embedding": [P, P, I, P, P, P, P, P, P, L, I, P, I, I, I, I, L, L, P, P],
+            "ie_sandwich_norm": [P, P, I, L, P, P, F, P, F, P, I, P, I, I, P],
+            "ie_silu_mul_bias": [P, P, P, I, I, I, P],
+            "ie_concat_cast": [P, P, P, I, I, I, P],
+            "ie_weighted_sum": [P, F, P, F, P, L, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -855,7 +860,7 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, hd, hd, page_size,
-            k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
+            k_cache.shape[0], scale, window, 0, None, self._err_ptr, self._stream()), "paged_attention")
 
     @_kind("attention.latent")
     def latent_paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, value_dim,
@@ -890,8 +895,8 @@ class CudaOps:
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, value_dim,
-            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, self._err_ptr, self._stream()),
-            "paged_attention_latent")
+            v_cache.shape[-1], page_size, k_cache.shape[0], scale, window, 0, None, self._err_ptr,
+            self._stream()), "paged_attention_latent")
 
     # --- kernels of single mixers and feed-forwards (libraries built on first use) -------------
 
@@ -915,6 +920,16 @@ class CudaOps:
             "ie_routed_align": "P I I P P P I P",
             "ie_routed_gate_up": "P P P I P P P I I I I F I F F P",
             "ie_routed_down": "P P P P I P P P I I I I I P",
+        },
+        "recurrent": {
+            "ie_short_conv_residual": "P I P P L P P P P I I I I I P P",
+            "ie_hgrn2_gates": "P I P P P I I P",
+            "ie_mlstm_gates": "P P I P P F P L L P P P I I I P",
+            "ie_gated_recurrence": "P I P I P I P P I P L P P P I I I I I F I P",
+            "ie_recurrence_readout": "P I P P I F P I P I L I I P",
+        },
+        "gated_attn": {
+            "ie_qk_norm_rope_write": "P I P P I I P P F P P P I P I I I I I I I P P",
         },
     }
 
@@ -1059,6 +1074,143 @@ class CudaOps:
             y.data_ptr(), w.data_ptr(), out.data_ptr(), weights.data_ptr(), _dtype_code(y),
             sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, n, ff, hidden,
             self._stream()), "routed_down")
+
+    # --- residual-stream operations of models with norms on both sides of a sublayer ------------
+
+    @_kind("embedding")
+    def bigram_embedding(self, embed, bigram, ids, ctx, state, slots, out, buckets, mul_prev, mul_cur) -> None:
+        """``out[n] = embed[id] + bigram[(prev * mul_prev + id * mul_cur) mod buckets]`` (row ``buckets``
+        for a request's first token).  ``state``: ``[slots, 1]``, the request's last token as the
+        integer's bits; moved on to the last token of this step."""
+        if bigram.shape[0] != buckets + 1 or bigram.dtype != embed.dtype or state.dtype != self.torch.float32:
+            raise KernelError("bigram_embedding: the table or the state does not fit")
+        self._check(self._bigram_embedding(
+            embed.data_ptr(), bigram.data_ptr(), _dtype_code(embed), ids.data_ptr(), ctx.positions.data_ptr(),
+            ctx.seq_of_token.data_ptr(), ctx.cu_q.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0),
+            state.shape[0], out.data_ptr(), ids.shape[0], embed.shape[1], embed.shape[0], buckets, mul_prev,
+            mul_cur, self._err_ptr, self._stream()), "bigram_embedding")
+
+    @_kind("norm")
+    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None) -> None:
+        """``y = delta (+ bias)``; ``y <- rms(y) * post_weight`` if given; ``h += y`` (not with
+        ``rows``); ``out = rms(h) * weight`` unless ``out`` is None.  ``delta`` may be None."""
+        n = h.shape[0] if rows is None else rows.shape[0]
+        parts, stride = self._partials(delta)
+        self._check(self._sandwich_norm(
+            h.data_ptr(), self._ptr(delta), parts, stride, self._ptr(bias), self._ptr(post_weight), post_eps,
+            self._ptr(weight), eps, self._ptr(out), _dtype_code(out) if out is not None else 0, self._ptr(rows), n,
+            h.shape[1], self._stream()), "sandwich_norm")
+
+    @_kind("activation")
+    def silu_mul_bias(self, gate_up, bias, out) -> None:
+        """``out = silu(g + bias_g) * (u + bias_u)`` from 32-bit rows of gates, then ups."""
+        if gate_up.dtype != self.torch.float32 or gate_up.shape[1] != 2 * out.shape[1]:
+            raise KernelError("silu_mul_bias reads 32-bit rows of gates and ups")
+        self._check(self._silu_mul_bias(gate_up.data_ptr(), self._ptr(bias), out.data_ptr(), _dtype_code(out),
+                                        out.shape[0], out.shape[1], self._stream()), "silu_mul_bias")
+
+    @_kind("stream")
+    def concat_cast(self, a, b, out) -> None:
+        """``out[n] = [a[n]; b[n]]`` from two 32-bit ``[N, width]`` arrays, in ``out``'s dtype."""
+        self._check(self._concat_cast(a.data_ptr(), b.data_ptr(), out.data_ptr(), _dtype_code(out), a.shape[0],
+                                      a.shape[1], self._stream()), "concat_cast")
+
+    @_kind("stream")
+    def weighted_sum(self, a, sa: float, b, sb: float, out) -> None:
+        """``out = sa * a + sb * b`` for contiguous 32-bit tensors of one shape."""
+        self._check(self._weighted_sum(a.data_ptr(), float(sa), b.data_ptr(), float(sb), out.data_ptr(), a.numel(),
+                                       self._stream()), "weighted_sum")
+
+    # --- recurrent mixers with a decaying matrix state -------------------------------------------
+
+    @_kind("recurrent.conv")
+    def short_conv_residual(self, x, w, state, slots, ctx, out) -> None:
+        """``out = x + conv(x)``: a causal convolution over time per channel (``w``: ``[channels, taps]``,
+        the last tap weighs the token itself); ``state``: ``[slots, (taps - 1) * channels]``, the
+        request's last inputs, moved on by the step's tokens."""
+        channels, taps = w.shape
+        if x.shape[1] != channels or state.shape[1] < (taps - 1) * channels or x.dtype != out.dtype:
+            raise KernelError("short_conv_residual: the sizes do not fit")
+        self._check(self._part_lib("recurrent").ie_short_conv_residual(
+            x.data_ptr(), _dtype_code(x), w.data_ptr(), state.data_ptr(), state.stride(0), slots.data_ptr(),
+            ctx.seq_of_token.data_ptr(), ctx.cu_q.data_ptr(), out.data_ptr(), x.shape[0], ctx.num_seqs, channels,
+            taps, state.shape[0], self._err_ptr, self._stream()), "short_conv_residual")
+        self.launches += 1 if taps > 1 else 0
+
+    @_kind("recurrent.gates")
+    def hgrn2_gates(self, proj, bias, lower, write, size) -> None:
+        """In the 32-bit projection ``[N, >= 2 size]``: ``q <- silu(q)``, ``f <- lower + (1 - lower) *
+        sigmoid(f + bias)``; ``write = 1 - f``."""
+        self._check(self._part_lib("recurrent").ie_hgrn2_gates(
+            proj.data_ptr(), proj.stride(0), bias.data_ptr(), lower.data_ptr(), write.data_ptr(), proj.shape[0],
+            size, self._stream()), "hgrn2_gates")
+
+    @_kind("recurrent.gates")
+    def mlstm_gates(self, gi, gf, bias_i, bias_f, cap, state, m_offset, slots, ctx, gates, heads) -> None:
+        """The exponential gates of the matrix memory from their pre-activations (views ``[N, heads]`` of
+        one projection), with the running maximum kept at ``state[slot, m_offset + head]``;
+        ``gates``: ``[N, heads, 3]`` = (decay, write gate, exp(-maximum))."""
+        if gi.stride(0) != gf.stride(0) or gi.stride(1) != 1 or gf.stride(1) != 1:
+            raise KernelError("mlstm_gates: the gates' pre-activations must be views of one projection")
+        self._check(self._part_lib("recurrent").ie_mlstm_gates(
+            gi.data_ptr(), gf.data_ptr(), gi.stride(0), bias_i.data_ptr(), bias_f.data_ptr(), float(cap),
+            state.data_ptr(), state.stride(0), m_offset, slots.data_ptr(), ctx.cu_q.data_ptr(), gates.data_ptr(),
+            ctx.num_seqs, heads, state.shape[0], self._stream()), "mlstm_gates")
+
+    @_kind("recurrent.rule")
+    def gated_recurrence(self, q, a, w, gates, v, state, slots, ctx, out, heads, dim, vdim, cols, q_scale) -> None:
+        """``S <- diag(a) S + w u^T; o = S^T q`` per head over every request's tokens of the step, from
+        and to its slot (``[heads, cols, dim]``).  ``q``, ``a``, ``w``: views ``[N, heads * dim]``;
+        ``v``: view ``[N, heads * vdim]``; with ``gates`` (``[N, heads, 3]``) ``a`` is the gates' decay,
+        ``u = gate * v``, and column ``vdim`` (if ``cols = vdim + 1``) carries the value 1."""
+        if dim > 512:
+            raise KernelError(f"the recurrence kernel takes key sizes up to 512, not {dim}")
+        self._check(self._part_lib("recurrent").ie_gated_recurrence(
+            q.data_ptr(), q.stride(0), self._ptr(a), 0 if a is None else a.stride(0), w.data_ptr(), w.stride(0),
+            self._ptr(gates), v.data_ptr(), v.stride(0), state.data_ptr(), state.stride(0), slots.data_ptr(),
+            ctx.cu_q.data_ptr(), out.data_ptr(), ctx.num_seqs, heads, dim, vdim, cols, float(q_scale),
+            state.shape[0], self._stream()), "gated_recurrence")
+
+    @_kind("recurrent.out")
+    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols) -> None:
+        """Per (token, head): with ``gates`` divide by ``max(|o[vdim]|, exp(-m)) + 1e-6``; divide by the
+        root mean square over ``vdim``; times ``weight`` (``[vdim]`` or ``[heads * vdim]``) and
+        ``sigmoid(gate_pre)`` (a view ``[N, heads * vdim]``) if given."""
+        per_head = 1 if weight.numel() == heads * vdim and heads > 1 else 0
+        if weight.numel() not in (vdim, heads * vdim):
+            raise KernelError("recurrence_readout: the weight fits neither a head nor all heads")
+        self._check(self._part_lib("recurrent").ie_recurrence_readout(
+            o.data_ptr(), cols, self._ptr(gates), weight.data_ptr(), per_head, eps, self._ptr(gate_pre),
+            0 if gate_pre is None else gate_pre.stride(0), out.data_ptr(), _dtype_code(out), o.shape[0] * heads,
+            heads, vdim, self._stream()), "recurrence_readout")
+
+    # --- attention with normalised queries and keys and sigmoid weights ---------------------------
+
+    @_kind("rotary+cache")
+    def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
+                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size) -> None:
+        if table is not None and table.shape[2] * 2 != rot_dims:
+            raise KernelError("rotary table does not match the rotated dims")
+        if proj.dtype != self.torch.float32 or proj.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim:
+            raise KernelError("qk_norm_rope_write reads the fused 32-bit projection of queries, keys and values")
+        self._check(self._part_lib("gated_attn").ie_qk_norm_rope_write(
+            proj.data_ptr(), proj.stride(0), positions.data_ptr(), self._ptr(table), rot_dims,
+            0 if table is None else table.shape[0], self._ptr(q_weight), self._ptr(k_weight), eps, q_out.data_ptr(),
+            k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), proj.shape[0],
+            heads, kv_heads, dim, vdim, page_size, k_cache.shape[0], self._err_ptr, self._stream()),
+            "qk_norm_rope_write")
+
+    @_kind("attention.sigmoid")
+    def sigmoid_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
+                          chunk, head_bias, out) -> None:
+        """Attention without a softmax: the weight of a visible key is ``sigmoid(score + head_bias[h])``;
+        a query sees the keys at or before it in its own chunk of ``chunk`` positions (0: all)."""
+        self._check(self._paged_attention_generic(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
+            block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
+            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, vdim, vdim, page_size,
+            k_cache.shape[0], scale, 0, int(chunk or 0), head_bias.data_ptr(), self._err_ptr, self._stream()),
+            "sigmoid_attention")
 
     @_kind("activation")
     def silu_mul(self, gate_up, out, interleave: int = 0) -> None:

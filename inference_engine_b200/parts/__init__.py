@@ -1,5 +1,6 @@
 from . import (  # noqa: F401 (register)
-    attention, block, delta_rule, embedding, feedforward, latent_attention, norm, position, routed,
+    attention, block, composite, delta_rule, embedding, feedforward, latent_attention, norm, position,
+    recurrent, routed, sigmoid_attention, stream,
 )
 from .base import (
     Block,

@@ -22,7 +22,12 @@ Categories and what each must provide
                   where ``h`` is the residual stream and ``delta`` the not-yet-added output of
                   the previous block, to be added times ``delta_scale``; ``residual_mult`` is the
                   factor its own returned delta is to be added with.
-``embedding``     ``forward(token_ids, ctx) -> h`` (32-bit residual stream).
+``embedding``     ``forward(token_ids, ctx) -> h`` (32-bit residual stream); one that keeps something
+                  per request (the previous token) says so with ``cache_request()`` and is given
+                  its binding as ``forward(token_ids, ctx, binding)``.
+``stream``        an operation on the whole residual stream between layers, named by a run-order
+                  entry's ``before``: ``forward(h, x0, ctx) -> None`` rewrites ``h`` in place
+                  (``x0``: the embedding's output, kept when a stream part asks for it).
 ``head``          ``forward(x, ctx) -> logits`` (32-bit ``[rows, vocab]``).
 """
 
@@ -59,6 +64,9 @@ class PagedKVRequest:
     # Size of a cached value row: None = as large as a key row; 0 = no value rows are kept (a
     # mixer whose values are a part of its key rows, such as a shared latent vector).
     value_dim: int | None = None
+    # A query sees only the keys of its own chunk of this many positions, counted from position 0
+    # (``None`` = no chunks): pages that lie wholly before the current chunk are given back.
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)
@@ -131,7 +139,10 @@ class PositionEncoding(Part):
 class Mixer(Part):
     category = "mixer"
 
-    def cache_request(self) -> PagedKVRequest | StateRequest | None:
+    def cache_request(self) -> PagedKVRequest | StateRequest | None | tuple:
+        """What the mixer keeps per request.  A mixer made of several (two side by side, one
+        wrapped around another) returns a tuple of requests, and is then handed a tuple of
+        bindings in the same order (``None`` where a request is ``None``)."""
         return None
 
     def forward(self, x, ctx, binding: CacheBinding | None):

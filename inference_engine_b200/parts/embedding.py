@@ -8,7 +8,7 @@ itself (engine/model/loader.py:91-92), one buffer.
 
 from __future__ import annotations
 
-from .base import BuildEnv, Part, WeightDecl
+from .base import BuildEnv, CacheBinding, Part, StateRequest, WeightDecl
 from .registry import register_part
 
 
@@ -35,6 +35,49 @@ class TokenEmbedding(Part):
 
         h = ctx.ws.buffer("residual", token_ids.shape[0], self.hidden_size, torch.float32)
         ctx.ops.embedding(self.table, token_ids, h)
+        return h
+
+
+@register_part("embedding", "token_bigram")
+class TokenBigramEmbedding(TokenEmbedding):
+    """Token embedding plus a hashed bigram embedding: row ``(previous * mul_prev + token * mul_cur)
+    mod buckets`` of a second table, whose last row (number ``buckets``) serves a request's first
+    token.  The token before a step's first one is part of the request's state: it lives in a
+    state slot on the device (the integer's bits in a 32-bit word), so a step launched on tokens
+    the device is still sampling finds it too."""
+
+    def __init__(self, weight: str, bigram: str, vocab_size: int, hidden_size: int, dtype, buckets: int,
+                 mul_prev: int, mul_cur: int) -> None:
+        super().__init__(weight, vocab_size, hidden_size, dtype)
+        if buckets < 1:
+            raise ValueError("the bigram table needs at least one bucket")
+        self.bigram_name, self.buckets = bigram, int(buckets)
+        self.mul_prev, self.mul_cur = int(mul_prev), int(mul_cur)
+        self.bigram = None
+
+    @classmethod
+    def from_spec(cls, params: dict, env: BuildEnv, **_):
+        return cls(params["weight"], params["bigram"], params["vocab_size"], env.hidden_size, env.torch_dtype,
+                   params["buckets"], params["mul_prev"], params["mul_cur"])
+
+    def weights(self) -> dict[str, WeightDecl]:
+        return {**super().weights(),
+                self.bigram_name: WeightDecl((self.buckets + 1, self.hidden_size), "table")}
+
+    def bind(self, tensors, env: BuildEnv) -> None:
+        super().bind(tensors, env)
+        self.bigram = tensors[self.bigram_name].to(self.dtype).contiguous()
+
+    def cache_request(self) -> StateRequest:
+        return StateRequest((1,))
+
+    def forward(self, token_ids, ctx, binding: CacheBinding):
+        import torch
+
+        group = ctx.groups[binding.group]
+        h = ctx.ws.buffer("residual", token_ids.shape[0], self.hidden_size, torch.float32)
+        ctx.ops.bigram_embedding(self.table, self.bigram, token_ids, ctx, group.state[binding.slot], group.slots,
+                                 h, self.buckets, self.mul_prev, self.mul_cur)
         return h
 
 

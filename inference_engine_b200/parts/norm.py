@@ -13,29 +13,54 @@ from .registry import register_part
 
 @register_part("norm", "rms")
 class RMSNorm(Norm):
-    def __init__(self, weight: str, size: int, eps: float, dtype) -> None:
+    """``offset``: what is added to the stored weight (1 for weights stored around zero, so that the
+    factor is ``1 + w``; 0 for weights stored around one)."""
+
+    def __init__(self, weight: str, size: int, eps: float, dtype, offset: float = 0.0) -> None:
         self.weight_name, self.size, self.eps, self.dtype = weight, int(size), float(eps), dtype
+        self.offset = float(offset)
         self.weight = None
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
         return cls(params["weight"], params.get("size", env.hidden_size), params["eps"],
-                   env.torch_dtype)
+                   env.torch_dtype, params.get("offset", 0.0))
 
     def weights(self) -> dict[str, WeightDecl]:
-        return {self.weight_name: WeightDecl((self.size,), "vector", "ones_plus_normal")}
+        init = "normal" if self.offset else "ones_plus_normal"
+        return {self.weight_name: WeightDecl((self.size,), "vector", init)}
 
     def bind(self, tensors, env: BuildEnv) -> None:
-        self.weight = tensors[self.weight_name].float().contiguous()
+        self.weight = (tensors[self.weight_name].float() + self.offset).contiguous()
 
-    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm", delta_scale: float = 1.0):
+    def add_norm(self, h, delta, ctx, rows=None, tag: str = "norm", delta_scale: float = 1.0,
+                 delta_post: "PostNorm | None" = None):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.buffer(tag, n, self.size, self.dtype)
-        if delta_scale == 1.0:
+        if delta_post is not None:
+            # the delta is normalised (and takes its bias) before it is added: one kernel for that,
+            # the add and this norm
+            if delta_scale != 1.0:
+                raise ValueError("a delta that is normalised before the add has no residual multiplier")
+            ctx.ops.sandwich_norm(h, delta, delta_post.bias, delta_post.norm.weight, delta_post.norm.eps,
+                                  self.weight, self.eps, out, rows)
+        elif delta_scale == 1.0:
             ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows)
         else:
             ctx.ops.rmsnorm(h, delta, self.weight, self.eps, out, rows, delta_scale=float(delta_scale))
         return out
+
+
+class PostNorm:
+    """What a block wants done to a sublayer's output before it enters the residual stream: a bias
+    (or None), then an RMS norm.  Carried beside the pending delta to whoever adds it."""
+
+    def __init__(self, norm: RMSNorm, bias=None) -> None:
+        self.norm, self.bias = norm, bias
+
+    def settle(self, h, delta, ctx) -> None:
+        """``h += norm(delta + bias)`` with no normalised output."""
+        ctx.ops.sandwich_norm(h, delta, self.bias, self.norm.weight, self.norm.eps, None, 0.0, None)
 
 
 @register_part("norm", "layer")

@@ -42,7 +42,7 @@ class RotaryEncoding(PositionEncoding):
     LAYOUTS = ("halves", "interleaved")
 
     def __init__(self, rotary_dim: int, theta: float, scaling: dict | None,
-                 max_positions: int, layout: str = "halves") -> None:
+                 max_positions: int, layout: str = "halves", angles: str = "float32") -> None:
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim ({rotary_dim}) must be even")
         if layout not in self.LAYOUTS:
@@ -50,6 +50,11 @@ class RotaryEncoding(PositionEncoding):
         # which entries form the pair rotated by angle j: "halves": j and j + rotary_dim/2 (Llama's);
         # "interleaved": 2j and 2j + 1.  The table of angles is the same; the consumer reads `layout`.
         self.layout = layout
+        if angles not in ("float32", "float64"):
+            raise ValueError(f"rotary angles are computed in float32 or float64, not {angles!r}")
+        # "float64": frequencies theta^(-2j/dim), angles and their cos and sin are worked out in
+        # 64-bit and rounded once to the 32-bit table (no frequency scaling in this mode)
+        self.angles = angles
         self.rotary_dim, self.theta, self.scaling = int(rotary_dim), float(theta), scaling
         self.max_positions = int(max_positions)
         self.inv_freq = self._table = None
@@ -57,13 +62,22 @@ class RotaryEncoding(PositionEncoding):
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
         return cls(params["rotary_dim"], params["theta"], params.get("scaling"),
-                   env.max_positions, params.get("layout", "halves"))
+                   env.max_positions, params.get("layout", "halves"), params.get("angles", "float32"))
 
     def bind(self, tensors, env: BuildEnv) -> None:
         """No stored tensor (the reference keeps ``inv_freq`` out of checkpoints,
         engine/model/layers.py:52-53): the table is computed here, on the device."""
         import torch
 
+        if self.angles == "float64":
+            if self.scaling:
+                raise ValueError("64-bit rotary angles take no frequency scaling")
+            j = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
+            inv_freq = torch.exp(-(j / self.rotary_dim) * math.log(self.theta))
+            freqs = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
+            self.inv_freq = inv_freq.float().to(env.device)
+            self._table = torch.stack((freqs.cos(), freqs.sin()), dim=1).float().contiguous().to(env.device)
+            return
         self.inv_freq = rotary_inv_freq(self.rotary_dim, self.theta, self.scaling).to(env.device)
         pos = torch.arange(self.max_positions, device=env.device).float()
         freqs = pos[:, None] * self.inv_freq.float()[None, :]

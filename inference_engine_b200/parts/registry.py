@@ -12,7 +12,7 @@ from typing import Any
 from ..config.spec import PartSpec
 from .base import BuildEnv
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

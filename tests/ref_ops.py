@@ -168,6 +168,170 @@ class RefOps:
                 out[j, t] = weights[t, j] * (y @ w_down[e].float().t())
         return out
 
+    # --- residual-stream operations of models with norms on both sides of a sublayer ------------
+
+    def bigram_embedding(self, embed, bigram, ids, ctx, state, slots, out, buckets, mul_prev, mul_cur):
+        tokens = ids.tolist()
+        words = state.view(torch.int32)  # the request's previous token, as the integer's bits
+        slot_list = slots.tolist()
+        for start, n, first_pos, slot in zip(ctx.q_starts, ctx.q_lens, ctx.start_positions, slot_list):
+            if n == 0:
+                continue
+            for t in range(start, start + n):
+                if first_pos + (t - start) == 0:
+                    row = buckets
+                else:
+                    prev = tokens[t - 1] if t > start else int(words[slot, 0])
+                    row = (prev * mul_prev + tokens[t] * mul_cur) % buckets
+                out[t] = embed[tokens[t]].float() + bigram[row].float()
+            words[slot, 0] = tokens[start + n - 1]
+        real = sum(ctx.q_lens)
+        if real < ids.shape[0]:  # the padding of a fixed-size launch: position 0
+            out[real:] = embed[ids[real:].long()].float() + bigram[buckets].float()
+
+    def sandwich_norm(self, h, delta, bias, post_weight, post_eps, weight, eps, out, rows=None):
+        x = h if rows is None else h[rows.long()]
+        if delta is not None:
+            y = delta.sum(0) if delta.dim() == 3 else delta
+            if rows is not None:
+                y = y[rows.long()]
+            if bias is not None:
+                y = y + bias
+            if post_weight is not None:
+                y = post_weight * (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps))
+            if rows is None:
+                h.add_(y)
+                x = h
+            else:
+                x = x + y
+        if out is not None:
+            out.copy_((weight * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))).to(out.dtype))
+
+    def silu_mul_bias(self, gate_up, bias, out):
+        i = out.shape[1]
+        gu = gate_up.float() + (bias if bias is not None else 0.0)
+        g, u = gu[:, :i], gu[:, i:]
+        out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+
+    def concat_cast(self, a, b, out):
+        out.copy_(torch.cat([a, b], dim=-1).to(out.dtype))
+
+    def weighted_sum(self, a, sa, b, sb, out):
+        out.copy_(sa * a + sb * b)
+
+    # --- recurrent mixers with a decaying matrix state -------------------------------------------
+
+    def short_conv_residual(self, x, w, state, slots, ctx, out):
+        channels, taps = w.shape
+        for start, n, slot in zip(ctx.q_starts, ctx.q_lens, slots.tolist()):
+            if n == 0:
+                continue
+            tail = state[slot, : (taps - 1) * channels].view(taps - 1, channels)
+            seen = torch.cat([tail, x[start: start + n].float()])  # [taps - 1 + n, channels]
+            y = torch.zeros(n, channels)
+            for j in range(taps):
+                y += seen[j: j + n] * w[:, j]
+            out[start: start + n] = (x[start: start + n].float() + y).to(out.dtype)
+            if taps > 1:
+                state[slot, : (taps - 1) * channels] = seen[n:].reshape(-1)
+
+    def hgrn2_gates(self, proj, bias, lower, write, size):
+        q, f = proj[:, :size], proj[:, size: 2 * size]
+        q.copy_(q * torch.sigmoid(q))
+        f.copy_(lower + (1 - lower) * torch.sigmoid(f + bias))
+        write.copy_(1 - f)
+
+    def mlstm_gates(self, gi, gf, bias_i, bias_f, cap, state, m_offset, slots, ctx, gates, heads):
+        g = gates.view(-1, heads, 3)
+        for start, n, slot in zip(ctx.q_starts, ctx.q_lens, slots.tolist()):
+            if n == 0:
+                continue
+            m = state[slot, m_offset: m_offset + heads].clone()
+            for t in range(start, start + n):
+                li = cap * torch.tanh((gi[t] + bias_i) / cap)
+                lf = torch.nn.functional.logsigmoid(cap * torch.tanh((gf[t] + bias_f) / cap))
+                m_new = torch.maximum(lf + m, li)
+                g[t, :, 0] = torch.exp(lf + m - m_new)
+                g[t, :, 1] = torch.exp(li - m_new)
+                g[t, :, 2] = torch.exp(-m_new)
+                m = m_new
+            state[slot, m_offset: m_offset + heads] = m
+
+    def gated_recurrence(self, q, a, w, gates, v, state, slots, ctx, out, heads, dim, vdim, cols, q_scale):
+        matrix = heads * cols * dim
+        o = out.view(-1, heads, cols)
+        for start, n, slot in zip(ctx.q_starts, ctx.q_lens, slots.tolist()):
+            if n == 0:
+                continue
+            S = state[slot, :matrix].view(heads, cols, dim).transpose(1, 2).clone()  # [heads, dim, cols]
+            for t in range(start, start + n):
+                qt, wt = q[t].view(heads, dim), w[t].view(heads, dim)
+                u = v[t].view(heads, vdim)
+                if cols > vdim:
+                    u = torch.cat([u, torch.ones(heads, 1)], dim=-1)
+                if gates is not None:
+                    g = gates[t].view(heads, 3)
+                    S = g[:, 0, None, None] * S + wt[:, :, None] * (g[:, 1, None] * u)[:, None, :]
+                else:
+                    S = a[t].view(heads, dim)[:, :, None] * S + wt[:, :, None] * u[:, None, :]
+                o[t] = torch.einsum("hdc,hd->hc", S, qt) * q_scale
+            state[slot, :matrix] = S.transpose(1, 2).reshape(-1)
+
+    def recurrence_readout(self, o, gates, weight, eps, gate_pre, out, heads, vdim, cols):
+        x = o.view(-1, heads, cols)
+        y = x[..., :vdim]
+        if gates is not None:
+            den = torch.maximum(x[..., vdim].abs(), gates.view(-1, heads, 3)[..., 2]) + 1e-6
+            y = y / den[..., None]
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+        y = y * (weight.view(heads, vdim) if weight.numel() == heads * vdim else weight)
+        if gate_pre is not None:
+            y = y * torch.sigmoid(gate_pre.float().reshape(-1, heads, vdim))
+        out.copy_(y.reshape(out.shape).to(out.dtype))
+
+    # --- attention with normalised queries and keys and sigmoid weights ---------------------------
+
+    def qk_norm_rope_write(self, proj, positions, table, rot_dims, q_weight, k_weight, eps, q_out, k_cache,
+                           v_cache, slot_mapping, heads, kv_heads, dim, vdim, page_size):
+        n = proj.shape[0]
+        q = proj[:, : heads * dim].reshape(n, heads, dim).float()
+        k = proj[:, heads * dim: (heads + kv_heads) * dim].reshape(n, kv_heads, dim).float()
+        v = proj[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim).float()
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+        if table is not None and rot_dims > 0:
+            half = rot_dims // 2
+            cos, sin = table[positions.long(), 0][:, None, :], table[positions.long(), 1][:, None, :]
+
+            def rot(x):
+                x1, x2, rest = x[..., :half], x[..., half:rot_dims], x[..., rot_dims:]
+                return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin, rest), dim=-1)
+
+            q, k = rot(q), rot(k)
+        q_out.copy_(q.reshape(n, heads * dim).to(q_out.dtype))
+        if slot_mapping is not None:
+            slots = slot_mapping.long()
+            page, offset = slots // page_size, slots % page_size
+            k_cache[page, :, offset] = k.to(k_cache.dtype)
+            v_cache[page, :, offset] = v.to(v_cache.dtype)
+
+    def sigmoid_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
+                          chunk, head_bias, out):
+        groups = nh // nkv
+        tables = block_tables.long().cpu()
+        positions = ctx.positions.cpu().tolist()
+        seqs = ctx.seq_of_token.cpu().tolist()
+        for t in range(ctx.num_tokens):
+            p, s = positions[t], seqs[t]
+            lo = (p // chunk) * chunk if chunk else 0
+            keys = torch.arange(lo, p + 1)
+            pages, offs = tables[s][keys // page_size], keys % page_size
+            k = k_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)  # [keys, nh, hd]
+            v = v_cache[pages, :, offs].float().repeat_interleave(groups, dim=1)
+            scores = torch.einsum("hd,khd->hk", q[t].reshape(nh, hd).float(), k) * scale
+            weights = torch.sigmoid(scores + head_bias[:, None])
+            out[t] = torch.einsum("hk,khd->hd", weights, v).reshape(nh * vdim).to(out.dtype)
+
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         if out is None:
             out = ws.buffer(tag, x.shape[0], w.shape[0], out_dtype)
