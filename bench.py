@@ -495,12 +495,84 @@ def design_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, ct
         rows[kind] = out
     return rows
 
+# --- the Ravapel design beside the closest models ------------------------------------------------
+
+RAVAPEL_SIZES = {
+    # width, (hgrn2: heads, dim, vdim), (attention: heads, kv_heads, dim, vdim, chunk, rotated dims),
+    # (matrix memory: heads, dim, vdim), dense ff, taps
+    "w1024": (1024, (8, 128, 128), (16, 4, 64, 64, 512, 32), (8, 64, 128), 4096, 4),
+    "w2048": (2048, (16, 128, 128), (16, 4, 128, 128, 1024, 64), (16, 64, 128), 8192, 4),
+}
+
+
+def ravapel_config(size: str) -> dict:
+    width, hg, at, mm, ff, taps = RAVAPEL_SIZES[size]
+    hgrn2 = {"heads": hg[0], "dim": hg[1], "vdim": hg[2]}
+    parallel = {"left": {"heads": at[0], "kv_heads": at[1], "dim": at[2], "vdim": at[3], "scale": at[2] ** -0.5,
+                         "mask": {"size": at[4]}, "rot": {"base": 10000.0, "dims": at[5]}},
+                "right": {"heads": mm[0], "dim": mm[1], "vdim": mm[2], "gate_cap": 15.0},
+                "left_scale": 0.7, "right_scale": 0.7}
+    dense = {"kind": "dense", "ff": ff}
+    layers = [("hgrn2", hgrn2), ("parallel", parallel), ("parallel", parallel), ("hgrn2", hgrn2)]
+    return {"architecture": "Ravapel", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
+            "norm": {"eps": 1e-6}, "canon": {"taps": taps},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+            "loop": {"start": 1, "stop": 3, "times": 1},
+            "layers": [{"type": t, "mixer": m, "mlp": dense} for t, m in layers]}
+
+
+def ravapel_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, ctx: float, decode: bool) -> dict:
+    """Per kind of kernel of the Ravapel model: microseconds per launch and, where the kind has such a
+    figure, what it is of the measured peak: decode launches against the copy rate for the bytes they
+    must read (weights, cached rows of the current chunk, state read and written), prompt launches
+    against the burst bf16 rate for their flops (the recurrences and 32-bit stages: the time only)."""
+    width, hg, at, mm, ff, taps = RAVAPEL_SIZES[size]
+    H, G, d, dv, chunk, _ = at
+    weights = {  # elements of the matrix a launch reads
+        "linear:hgrn2.in": width * hg[0] * (2 * hg[1] + hg[2]), "linear:hgrn2.delta": width * hg[0] * hg[2],
+        "linear:sigattn.qkv": width * ((H + G) * d + G * dv), "linear:sigattn.delta": width * H * dv,
+        "linear:mlstm.in": width * mm[0] * (2 * mm[1] + 2 * mm[2] + 2), "linear:mlstm.delta": width * mm[0] * mm[2],
+        "linear:ffn.gate_up32": 2 * width * ff, "linear:ffn.delta": width * ff,
+        "linear:stream.reinject": 2 * width * width, "linear:head": width * DESIGN_VOCAB,
+    }
+    # the two recurrences share a kind; two layers of each: state floats read and written per request
+    state = (hg[0] * hg[1] * hg[2] + mm[0] * mm[1] * (mm[2] + 1)) / 2
+    keys_decode = (ctx % chunk) + 1  # keys of the current chunk
+    rows = {}
+    for kind, r in kinds.items():
+        us = r["ms"] / r["launches"] * 1e3
+        out = {"us": round(us, 2), "launches": r["launches"]}
+        if decode:
+            nbytes = None
+            if weights.get(kind):
+                nbytes = 2 * weights[kind]
+            elif kind == "attention.sigmoid":
+                nbytes = batch * keys_decode * G * (d + dv) * 2
+            elif kind == "recurrent.rule":
+                nbytes = batch * state * 4 * 2
+            if nbytes:
+                out.update(gbs=round(nbytes / (us * 1e-6) / 1e9, 1),
+                           frac=round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4))
+        else:
+            f = None
+            if kind == "attention.sigmoid":  # a chunk's queries see half of its keys on average
+                f = 2.0 * tokens * min(chunk, tokens) / 2 * H * (d + dv)
+            elif weights.get(kind) and kind != "linear:head":
+                f = 2.0 * tokens * weights[kind]
+            if f:
+                out.update(tflops=round(f / (us * 1e-6) / 1e12, 1),
+                           frac=round(f / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4))
+        rows[kind] = out
+    return rows
+
 
 def run_design(args) -> dict:
     """`--design rugedra`: prompt and decode throughput of the Rugedra design at layer sizes of a real
     model's (four layers: latent attention + dense, delta rule + experts, latent attention + experts,
     delta rule + dense; random weights), beside a Llama model of the same width, depth, feed-forward
-    size and vocabulary, and every kind of kernel of both by itself."""
+    size and vocabulary, and every kind of kernel of both by itself.  `--design ravapel`: the Ravapel
+    design (four layers: HGRN2, two of attention beside a matrix memory, HGRN2, all with a dense
+    feed-forward; the middle two as a loop of one pass) beside the Rugedra and the Llama model."""
     import torch
 
     from inference_engine_b200.engine.llm_engine import LLMEngine
@@ -515,7 +587,10 @@ def run_design(args) -> dict:
     sampler.start()
     out = {}
     for size in args.sizes.split(","):
-        for name, cfg in (("rugedra", rugedra_config(size)), ("llama", llama_config_like(size))):
+        models = [("rugedra", rugedra_config(size)), ("llama", llama_config_like(size))]
+        if args.design == "ravapel":
+            models.insert(0, ("ravapel", ravapel_config(size)))
+        for name, cfg in models:
             engine = LLMEngine.from_random(
                 cfg, seed=0, dtype="bfloat16", device="cuda", max_model_len=MAX_CONTEXT,
                 num_blocks=-(-tokens_needed // BLOCK_SIZE), block_size=BLOCK_SIZE, max_num_seqs=max(batch, 8),
@@ -527,7 +602,10 @@ def run_design(args) -> dict:
                    "prefill_tokens_per_s": round(PREFILL_LEN / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
                    # (the prompt step is launched eagerly: what its kernels take by themselves, without the host)
                    "prefill_kernels_ms": round(sum(r["ms"] for r in kinds_prefill.values()), 3)}
-            if name == "rugedra":
+            if name == "ravapel":
+                row["kernels"] = {f"decode_b{batch}": ravapel_rows(size, kinds, peaks, batch, batch, ctx, True),
+                                  f"prefill_{PREFILL_LEN}": ravapel_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
+            elif name == "rugedra":
                 row["kernels"] = {f"decode_b{batch}": design_rows(size, kinds, peaks, batch, batch, ctx, True),
                                   f"prefill_{PREFILL_LEN}": design_rows(size, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False)}
             else:
@@ -536,7 +614,7 @@ def run_design(args) -> dict:
             out[f"{name}_{size}"] = row
             del engine
             torch.cuda.empty_cache()
-    return {"design": "rugedra", "beside": "llama of equal width, depth, feed-forward size and vocabulary",
+    return {"design": args.design, "beside": "models of equal width, depth, feed-forward size and vocabulary",
             "batch": batch, "decode_context": PROMPT_LEN, "prefill_tokens": PREFILL_LEN, "dtype": "bf16",
             "data": "synthetic: seeded random weights N(0, 0.02), uniform-random token ids",
             "peaks": peaks_kind, "models": out, "clocks": sampler.stop()}
@@ -658,7 +736,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--design", default=None, choices=["rugedra"],
+    ap.add_argument("--design", default=None, choices=["rugedra", "ravapel"],
                     help="instead of the default workload: this design at real layer sizes beside the closest "
                          "model the engine had, prompt and decode throughput and every kind of kernel")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: which of " + ",".join(DESIGN_SIZES))

@@ -41,6 +41,28 @@ def _float32_bound(cfg, weights, requests, want) -> dict:
     return dict(atol=max(3 * worst, H.TOL["float32"]["atol"]), rtol=H.TOL["float32"]["rtol"])
 
 
+def _bfloat16_bound(tmp_path, cfg, weights, requests, want) -> dict:
+    """The bfloat16 bound of a configuration: three times what rounding does to the same requests
+    on the plain stand-ins of the kernels run in bfloat16 (activations rounded between the parts,
+    as the kernels round them), and never below the fixed bounds.  Peaked sigmoid weights and
+    several passes over the same layers make a few positions move by a tenth under rounding
+    alone; a lost or wrongly seen key moves them by several tenths."""
+    from tests.ref_ops import RefOps
+
+    room = sum(H.round64(len(t)) for t in requests.values())
+    got = H.collect(_session(tmp_path / "bound", cfg, weights, "bfloat16", "cpu", RefOps(), room, 16),
+                    H.trace_whole(requests))
+    tol = dict(BF16_TOL)
+    for rid in requests:
+        diff = (got[rid].double() - want[rid].double()).abs()
+        pos_rel = diff.pow(2).mean(-1).sqrt() / want[rid].double().pow(2).mean(-1).sqrt().clamp_min(1e-12)
+        rel = float(diff.pow(2).mean().sqrt() / want[rid].double().pow(2).mean().sqrt())
+        tol["atol"] = max(tol["atol"], 3 * float(diff.max()))
+        tol["pos_rel_rms"] = max(tol["pos_rel_rms"], 3 * float(pos_rel.max()))
+        tol["rel_rms"] = max(tol["rel_rms"], 3 * rel)
+    return tol
+
+
 def _session(tmp_path, cfg, weights, dtype, device, ops, max_tokens, page_size):
     from inference_engine_b200.engine.replay import ReplaySession
 
@@ -53,7 +75,8 @@ def _run_all_modes(tmp_path, name, dtype, device, ops, page_size=4, lengths=LENG
     weights = R.make_weights(cfg, seed=11)
     requests = _requests(cfg, lengths)
     want = _want(cfg, weights, requests)
-    tol = _float32_bound(cfg, weights, requests, want) if dtype == "float32" else BF16_TOL
+    tol = (_float32_bound(cfg, weights, requests, want) if dtype == "float32"
+           else _bfloat16_bound(tmp_path, cfg, weights, requests, want))
     mixed, peak = H.trace_mixed(requests, seed=5, tail=7, max_portion=15)
     whole_room = sum(H.round64(len(t)) for t in requests.values())
     results = {}
@@ -407,7 +430,8 @@ def test_long_decoding_through_state_and_pages(tmp_path, dtype):
     session = _session(tmp_path, cfg, weights, dtype, "cuda", get_ops("cuda"), 448, 16)
     got = H.collect(session, H.trace_decode_tail({"a": toks}, 400))["a"]
     H.assert_close(got, want, dtype, "long decoding",
-                   _float32_bound(cfg, weights, {"a": toks}, {"a": want}) if dtype == "float32" else BF16_TOL)
+                   _float32_bound(cfg, weights, {"a": toks}, {"a": want}) if dtype == "float32"
+                   else _bfloat16_bound(tmp_path, cfg, weights, {"a": toks}, {"a": want}))
 
 
 def _greedy_plain(cfg, weights, prompt, count):
