@@ -26,7 +26,7 @@ __device__ __forceinline__ float silu_f(float y) { return y / (1.0f + expf(-y));
 __device__ __forceinline__ float sigmoid_f(float y) { return 1.0f / (1.0f + expf(-y)); }
 __device__ __forceinline__ float logsigmoid_f(float y) { return fminf(y, 0.f) - log1pf(expf(-fabsf(y))); }
 
-// grid: tokens.  x and out: [N, channels] in the compute dtype; w: [channels, taps], the last tap
+// grid: (tokens, blocks of channels).  x and out: [N, channels] in the compute dtype; w: [channels, taps], the last tap
 // weighs the token itself; tail: the slot's kept inputs [taps - 1][channels], oldest first.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -45,7 +45,7 @@ short_conv_residual_kernel(const T* __restrict__ x, const float* __restrict__ w,
         return;
     }
     const float* tail = state + (size_t)slot * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < taps; ++j) {
             int back = taps - 1 - j;
@@ -57,7 +57,7 @@ short_conv_residual_kernel(const T* __restrict__ x, const float* __restrict__ w,
     }
 }
 
-// One block per request of the step: the kept inputs become the last taps - 1 of (kept, new).
+// grid: (requests of the step, blocks of channels): the kept inputs become the last taps - 1 of (kept, new).
 template <typename T>
 __global__ void short_conv_tail_kernel(const T* __restrict__ x, float* __restrict__ state, long long state_stride,
                                        const int* __restrict__ slots, const int* __restrict__ cu_q, int channels,
@@ -69,7 +69,7 @@ __global__ void short_conv_tail_kernel(const T* __restrict__ x, float* __restric
     int slot = slots[seq];
     if (len <= 0 || slot < 0 || slot >= num_slots) return;
     float* tail = state + (size_t)slot * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         // a thread owns a channel and goes through the rows in rising order, so a kept row is
         // read before it is overwritten
         for (int j = 0; j < taps - 1; ++j) {
@@ -331,19 +331,23 @@ IE_API int ie_short_conv_residual(const void* x, int dtype, const float* w, floa
     if (taps < 1) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     int e;
+    // few tokens: a thread per channel; many: a few channels per thread
+    int per_row = (channels + 255) / 256;
+    int cb = num_tokens >= 512 ? (per_row < 2 ? per_row : 2) : per_row;
+    dim3 grid(num_tokens, cb), tail_grid(num_seqs, per_row);
     if (dtype == IE_BF16)
-        e = ie_launch(short_conv_residual_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), 0, s,
+        e = ie_launch(short_conv_residual_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                       (const __nv_bfloat16*)x, w, (const float*)state, state_stride, slots, seq_of_token, cu_q,
                       (__nv_bfloat16*)out, channels, taps, num_slots, err);
     else
-        e = ie_launch(short_conv_residual_kernel<float>, dim3(num_tokens), dim3(256), 0, s, (const float*)x, w,
+        e = ie_launch(short_conv_residual_kernel<float>, grid, dim3(256), 0, s, (const float*)x, w,
                       (const float*)state, state_stride, slots, seq_of_token, cu_q, (float*)out, channels, taps,
                       num_slots, err);
     if (e != 0 || taps < 2) return e;
     if (dtype == IE_BF16)
-        return ie_launch(short_conv_tail_kernel<__nv_bfloat16>, dim3(num_seqs), dim3(256), 0, s,
+        return ie_launch(short_conv_tail_kernel<__nv_bfloat16>, tail_grid, dim3(256), 0, s,
                          (const __nv_bfloat16*)x, state, state_stride, slots, cu_q, channels, taps, num_slots);
-    return ie_launch(short_conv_tail_kernel<float>, dim3(num_seqs), dim3(256), 0, s, (const float*)x, state,
+    return ie_launch(short_conv_tail_kernel<float>, tail_grid, dim3(256), 0, s, (const float*)x, state,
                      state_stride, slots, cu_q, channels, taps, num_slots);
 }
 

@@ -70,13 +70,43 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return total;
 }
 
-template <typename OutT>
+template <int VEC>
+struct Pack { float v[VEC]; };
+template <int VEC>
+__device__ __forceinline__ Pack<VEC> load_pack(const float* p) {
+    Pack<VEC> r;
+    if (VEC == 4) {
+        float4 t = *reinterpret_cast<const float4*>(p);
+        r.v[0] = t.x; r.v[1 % VEC] = t.y; r.v[2 % VEC] = t.z; r.v[3 % VEC] = t.w;
+    } else {
+        r.v[0] = *p;
+    }
+    return r;
+}
+template <int VEC>
+__device__ __forceinline__ void store_pack(float* p, const Pack<VEC>& r) {
+    if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1 % VEC], r.v[2 % VEC], r.v[3 % VEC]);
+    else *p = r.v[0];
+}
+template <int VEC>
+__device__ __forceinline__ void store_pack(__nv_bfloat16* p, const Pack<VEC>& r) {
+    if (VEC == 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1 % VEC]), hi = __floats2bfloat162_rn(r.v[2 % VEC], r.v[3 % VEC]);
+        *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+    } else {
+        *p = __float2bfloat16_rn(r.v[0]);
+    }
+}
+
+// VEC = 4: rows whose width is a multiple of 4 move as 16-byte pieces (the sums are taken in the same
+// order for a given width either way: a thread adds its entries in rising order, then the block adds).
+template <typename OutT, int VEC>
 __global__ void __launch_bounds__(SN_THREADS)
 sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials, size_t partial_stride,
                      const float* __restrict__ bias, const float* __restrict__ post_w, float post_eps,
                      const float* __restrict__ pre_w, float pre_eps, OutT* __restrict__ out,
                      const int* __restrict__ rows, int hidden) {
-    extern __shared__ float row_buf[];  // [hidden]
+    extern __shared__ __align__(16) float row_buf[];  // [hidden]
     __shared__ float red[SN_THREADS / 32];
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -84,35 +114,56 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
     size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     float ss = 0.f;
     if (delta != nullptr) {
-        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
-            float y = delta[src + i];
-            for (int p = 1; p < num_partials; ++p) y += delta[p * partial_stride + src + i];
-            if (bias) y += bias[i];
-            row_buf[i] = y;
-            ss = fmaf(y, y, ss);
+        for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+            Pack<VEC> y = load_pack<VEC>(delta + src + i);
+            for (int p = 1; p < num_partials; ++p) {
+                Pack<VEC> d = load_pack<VEC>(delta + p * partial_stride + src + i);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) y.v[v] += d.v[v];
+            }
+            if (bias) {
+                Pack<VEC> b = load_pack<VEC>(bias + i);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) y.v[v] += b.v[v];
+            }
+            store_pack<VEC>(row_buf + i, y);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) ss = fmaf(y.v[v], y.v[v], ss);
         }
         float inv = 1.0f;
         if (post_w != nullptr) inv = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + post_eps);
         ss = 0.f;
-        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
-            float y = row_buf[i];
-            if (post_w != nullptr) y = post_w[i] * (y * inv);
-            float x = h[src + i] + y;
-            row_buf[i] = x;
-            if (rows == nullptr) h[src + i] = x;
-            ss = fmaf(x, x, ss);
+        for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+            Pack<VEC> y = load_pack<VEC>(row_buf + i), x = load_pack<VEC>(h + src + i);
+            if (post_w != nullptr) {
+                Pack<VEC> w = load_pack<VEC>(post_w + i);
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) y.v[v] = w.v[v] * (y.v[v] * inv);
+            }
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                x.v[v] += y.v[v];
+                ss = fmaf(x.v[v], x.v[v], ss);
+            }
+            store_pack<VEC>(row_buf + i, x);
+            if (rows == nullptr) store_pack<VEC>(h + src + i, x);
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += SN_THREADS) {
-            float x = h[src + i];
-            row_buf[i] = x;
-            ss = fmaf(x, x, ss);
+        for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+            Pack<VEC> x = load_pack<VEC>(h + src + i);
+            store_pack<VEC>(row_buf + i, x);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) ss = fmaf(x.v[v], x.v[v], ss);
         }
     }
     if (out == nullptr) return;
     float inv2 = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + pre_eps);
-    for (int i = threadIdx.x; i < hidden; i += SN_THREADS)
-        ie_store(out + (size_t)r * hidden + i, pre_w[i] * (row_buf[i] * inv2));
+    for (int i = threadIdx.x * VEC; i < hidden; i += SN_THREADS * VEC) {
+        Pack<VEC> x = load_pack<VEC>(row_buf + i), w = load_pack<VEC>(pre_w + i);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) x.v[v] = w.v[v] * (x.v[v] * inv2);
+        store_pack<VEC>(out + (size_t)r * hidden + i, x);
+    }
 }
 
 template <typename T>
@@ -190,23 +241,28 @@ IE_API int ie_sandwich_norm(float* h, const float* delta, int num_partials, long
     size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
+    bool vec = hidden % 4 == 0 && (size_t)partial_stride % 4 == 0 &&
+               ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(bias) |
+                 reinterpret_cast<uintptr_t>(post_w) | reinterpret_cast<uintptr_t>(pre_w) |
+                 reinterpret_cast<uintptr_t>(out)) % 16 == 0);
+#define IE_SN_LAUNCH(T, V)                                                                                         \
+    do {                                                                                                           \
+        static IePerDevice allowed;                                                                                \
+        if (smem > 48 * 1024) {                                                                                    \
+            cudaError_t e = ie_allow_smem(allowed, sandwich_norm_kernel<T, V>, 200 * 1024);                        \
+            if (e != cudaSuccess) return (int)e;                                                                   \
+        }                                                                                                          \
+        return ie_launch(sandwich_norm_kernel<T, V>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,          \
+                         num_partials, (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps, (T*)out,    \
+                         rows, hidden);                                                                            \
+    } while (0)
     if (out_dtype == IE_BF16) {
-        static IePerDevice allowed;
-        if (smem > 48 * 1024) {
-            cudaError_t e = ie_allow_smem(allowed, sandwich_norm_kernel<__nv_bfloat16>, 200 * 1024);
-            if (e != cudaSuccess) return (int)e;
-        }
-        return ie_launch(sandwich_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta,
-                         num_partials, (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps,
-                         (__nv_bfloat16*)out, rows, hidden);
+        if (vec) IE_SN_LAUNCH(__nv_bfloat16, 4);
+        IE_SN_LAUNCH(__nv_bfloat16, 1);
     }
-    static IePerDevice allowed32;
-    if (smem > 48 * 1024) {
-        cudaError_t e = ie_allow_smem(allowed32, sandwich_norm_kernel<float>, 200 * 1024);
-        if (e != cudaSuccess) return (int)e;
-    }
-    return ie_launch(sandwich_norm_kernel<float>, dim3(num_rows), dim3(SN_THREADS), smem, s, h, delta, num_partials,
-                     (size_t)partial_stride, bias, post_w, post_eps, pre_w, pre_eps, (float*)out, rows, hidden);
+    if (vec) IE_SN_LAUNCH(float, 4);
+    IE_SN_LAUNCH(float, 1);
+#undef IE_SN_LAUNCH
 }
 
 IE_API int ie_silu_mul_bias(const float* gate_up, const float* bias, void* out, int out_dtype, int num_rows,

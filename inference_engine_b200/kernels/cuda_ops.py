@@ -17,7 +17,8 @@ import functools
 import os
 from ctypes import c_float, c_int, c_void_p
 
-from .build import ATTENTION_HEAD_DIMS, build_attention, build_core, build_part_library
+from .build import (ATTENTION_HEAD_DIMS, build_attention, build_core, build_part_library,
+                    build_sigmoid_attention)
 
 _ERRORS = {
     1: "a token id outside the vocabulary",
@@ -123,6 +124,8 @@ class CudaOps:
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
         self._part_libs: dict[str, object] = {}
+        self._sigattn_libs: dict[tuple[int, int], object] = {}
+        self.sigmoid_mma = os.environ.get("IE_B200_SIGMOID_MMA", "1") != "0"  # tensor-core sigmoid attention
         self._argmax_scratch = None
         self._tickets = None
         self._retired_tickets = []
@@ -1200,11 +1203,42 @@ class CudaOps:
             heads, kv_heads, dim, vdim, page_size, k_cache.shape[0], self._err_ptr, self._stream()),
             "qk_norm_rope_write")
 
+    SIGMOID_MMA_MIN_PORTION = 32  # a step whose longest portion has this many tokens runs the tensor-core kernel
+
+    def _sigmoid_attention_lib(self, hd: int, vdim: int):
+        lib = self._sigattn_libs.get((hd, vdim))
+        if lib is None:
+            path = build_sigmoid_attention(hd, vdim)
+            try:
+                lib = ctypes.CDLL(str(path))
+            except OSError as exc:
+                raise KernelError(f"the kernel library {path} could not be loaded: {exc}") from exc
+            P, I, F = c_void_p, c_int, c_float
+            lib.ie_sigmoid_attention_mma.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P, P]
+            lib.ie_sigmoid_attention_mma.restype = c_int
+            self._sigattn_libs[(hd, vdim)] = lib
+        return lib
+
     @_kind("attention.sigmoid")
     def sigmoid_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, vdim, page_size, scale,
                           chunk, head_bias, out) -> None:
         """Attention without a softmax: the weight of a visible key is ``sigmoid(score + head_bias[h])``;
-        a query sees the keys at or before it in its own chunk of ``chunk`` positions (0: all)."""
+        a query sees the keys at or before it in its own chunk of ``chunk`` positions (0: all).
+        bfloat16 steps with a prompt portion of some length run the tensor-core kernel (key and value
+        sizes multiples of 16 up to 256, launched for the step's own lengths, so not in a captured
+        step); single tokens, 32-bit and other sizes the general kernel, whose order of operations
+        does not depend on the batch."""
+        if (self.sigmoid_mma and q.dtype == self.torch.bfloat16 and hd % 16 == 0 and vdim % 16 == 0
+                and 16 <= hd <= 256 and 16 <= vdim <= 256 and page_size & (page_size - 1) == 0
+                and getattr(ctx, "bounds", None) is None and not getattr(ctx, "padded", False)
+                and getattr(ctx, "max_q_len", 0) >= self.SIGMOID_MMA_MIN_PORTION):
+            lib = self._sigmoid_attention_lib(hd, vdim)
+            self._check(lib.ie_sigmoid_attention_mma(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(), ctx.num_seqs,
+                ctx.max_q_len, nh, nkv, page_size, k_cache.shape[0], scale, int(chunk or 0), head_bias.data_ptr(),
+                self._err_ptr, self._stream()), "sigmoid_attention_mma")
+            return
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),

@@ -194,7 +194,8 @@ def _ctx(lens, starts, device, slots=None):
     pos = [s + t for s, n in zip(starts, lens) for t in range(n)]
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)  # noqa: E731
     return SimpleNamespace(num_tokens=cu[-1], num_seqs=b, seq_of_token=i32(seq), positions=i32(pos), cu_q=i32(cu),
-                           q_starts=cu[:-1], q_lens=list(lens), start_positions=list(starts),
+                           q_starts=cu[:-1], q_lens=list(lens), start_positions=list(starts), max_q_len=max(lens),
+                           ctx_lens=i32([s + n for s, n in zip(starts, lens)]), bounds=None, padded=False,
                            slots=i32(slots if slots is not None else list(range(b))))
 
 
@@ -338,6 +339,54 @@ def test_sigmoid_attention_sees_exactly_its_chunk(device, chunk):
         seen = want.abs().amax((1, 2))
         inside, outside = 2 * chunk, 2 * chunk + 1  # an even position (looks just inside) and an odd one
         assert seen[inside] > 0.1 and seen[outside] < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,dv,chunk", [(16, 32, 50), (64, 64, None), (128, 128, 200), (48, 16, 64), (128, 64, 1)])
+def test_sigmoid_attention_on_the_tensor_cores(d, dv, chunk):
+    """The bfloat16 kernel for prompt portions against the plain function: portions that start and end
+    inside chunks and tiles, two requests of unequal length in one step (one of them a single token),
+    scattered pages, a key per query that stands out just inside or just outside the chunk."""
+    from inference_engine_b200.kernels import get_ops
+
+    ops, g = get_ops("cuda"), torch.Generator().manual_seed(d + dv)
+    T, H, G, ps = 333, 6, 2, 16
+    bf = lambda x: x.to(torch.bfloat16).float()  # noqa: E731
+    k = bf(torch.randn(T, G, d, generator=g) * 0.3)
+    v = bf(torch.randn(T, G, dv, generator=g))
+    q = bf(torch.randn(T, H, d, generator=g) * 0.3)
+    for t in range(0, T, 3):
+        first = (t // chunk) * chunk if chunk else 0
+        target = first if t % 2 == 0 else first - 1
+        if 0 <= target < T:
+            k[target, :, t % d] += 2.0
+            q[t, :, t % d] += 8.0
+    q, k = bf(q), bf(k)
+    bias = torch.linspace(-6.0, -2.0, H)
+    scale = 0.7
+    want = P.sigmoid_chunk_attention(q.double(), k.double(), v.double(), scale, bias.double(), chunk).float()
+    pages = -(-T // ps)
+    order = torch.randperm(pages + 3, generator=g).tolist()[:pages]
+    kc = _paged(k, ps, pages + 3, order, "cuda").to(torch.bfloat16)
+    vc = _paged(v, ps, pages + 3, order, "cuda").to(torch.bfloat16)
+    other = [pages + 3] * pages  # the second request: one token on the scratch page
+    tables = torch.tensor([order, other], dtype=torch.int32, device="cuda")
+    kc[pages + 3], vc[pages + 3] = 0.5, 0.25
+    before = ops.launch_counts.get("sigmoid_attention_mma", 0)
+    got, at = [], 0
+    for n in [70, 33, 130, 100]:
+        ctx = _ctx([n, 1], [at, 0], "cuda")
+        qq = torch.cat([q[at: at + n].reshape(n, -1), torch.ones(1, H * d)]).to("cuda", torch.bfloat16)
+        out = torch.zeros(n + 1, H * dv, device="cuda", dtype=torch.bfloat16)
+        ops.sigmoid_attention(qq, kc, vc, tables, ctx, H, G, d, dv, ps, scale, chunk, bias.cuda(), out)
+        got.append(out[:n].float().cpu().view(n, H, dv))
+        lone = torch.sigmoid(torch.tensor(d * 0.5 * scale) + bias)[:, None] * 0.25  # its one key and value
+        torch.testing.assert_close(out[n].float().cpu().view(H, dv), lone.expand(H, dv), atol=2e-2, rtol=2e-2)
+        at += n
+    ops.check_errors()
+    assert ops.launch_counts.get("sigmoid_attention_mma", 0) == before + 4  # (the kernel under test did run)
+    # weights are rounded to bfloat16 before the second product, outputs to bfloat16
+    torch.testing.assert_close(torch.cat(got), want, atol=0.06, rtol=0.03)
 
 
 @pytest.mark.parametrize("device", DEVICES)
