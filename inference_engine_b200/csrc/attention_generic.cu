@@ -115,27 +115,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
             for (int i = 0; i < MAX_ACC; ++i) acc[i] *= alpha;
         }
         int count = min(32, pos - t0 + 1);
-        // four keys at a time: their value rows are asked for together and added in rising order
-        for (int j0 = 0; j0 < count; j0 += 4) {
-            float pj[4];
-            long long rj[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                pj[u] = __shfl_sync(0xffffffffu, p, (j0 + u) & 31);
-                rj[u] = __shfl_sync(0xffffffffu, row, (j0 + u) & 31);
-                if (j0 + u >= count) rj[u] = -1;  // uniform across the warp
-            }
+        for (int j = 0; j < count; ++j) {
+            float pj = __shfl_sync(0xffffffffu, p, j);
+            long long rj = __shfl_sync(0xffffffffu, row, j);
+            if (rj < 0) continue;  // uniform across the warp
+            const T* vrow = v_cache + rj * v_stride;
 #pragma unroll
             for (int i = 0; i < MAX_ACC; ++i) {
                 int d = lane + 32 * i;
-                if (i < nacc && d < hdv) {
-                    float vv[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) vv[u] = rj[u] >= 0 ? ie_load(v_cache + rj[u] * v_stride + d) : 0.f;
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        if (rj[u] >= 0) acc[i] = fmaf(pj[u], vv[u], acc[i]);
-                }
+                if (i < nacc && d < hdv) acc[i] = fmaf(pj, ie_load(vrow + d), acc[i]);
             }
         }
         m = m_new;

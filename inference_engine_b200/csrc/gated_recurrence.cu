@@ -14,7 +14,7 @@
 // channel, the last taps - 1 inputs kept per request; hgrn2_gates; mlstm_gates (a warp per request
 // and head walks the step's tokens in order); gated_recurrence (columns of S do not interact: a
 // block owns some columns of one head of one request, TPC lanes a column, tokens in order, eight at
-// a time through shared memory with the next eight on their way); recurrence_readout (normaliser,
+// a time through a ring of four shared-memory buffers, three chunks on their way); recurrence_readout (normaliser,
 // unit root mean square per head, weight, output gate).  Every sum is taken in an order that
 // depends on the sizes alone, never on how a request's tokens were cut into steps or batched.
 #include "common.cuh"
@@ -147,6 +147,7 @@ mlstm_gates_kernel(const float* __restrict__ gi, const float* __restrict__ gf, i
 
 constexpr int GR_THREADS = 128;
 constexpr int GR_CHUNK = 8;  // tokens staged in shared memory at a time
+constexpr int GR_STAGES = 4;  // ... in a ring of so many buffers: three chunks are on their way while one is worked on
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -188,7 +189,7 @@ gated_recurrence_kernel(const float* __restrict__ q, int q_ld, const float* __re
         int r = sub + TPC * i;
         s[i] = (live && r < dim) ? S[r] : 0.f;
     }
-    for (int i = tid; i < 2 * BUF; i += GR_THREADS) sm[i] = 0.f;  // entries beyond dim read as zero
+    for (int i = tid; i < GR_STAGES * BUF; i += GR_THREADS) sm[i] = 0.f;  // entries beyond dim read as zero
     __syncthreads();
     int c0 = blockIdx.x * COLS;
     bool vec = (dim % 4 == 0) && (q_ld % 4 == 0) && (w_ld % 4 == 0) && (SCALAR || a_ld % 4 == 0) &&
@@ -227,14 +228,21 @@ gated_recurrence_kernel(const float* __restrict__ q, int q_ld, const float* __re
             cp_async4(gs + tid, gates + ((size_t)(start + t0 + (tid >> 1)) * heads + head) * 3 + (tid & 1));
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    stage(0, 0);
-    int b = 0;
+    // (a step of one chunk waits for its memory once; a prompt's chunks find theirs landed: with one
+    // chunk ahead every eight tokens cost a trip to memory, 0.25 us a token whatever the sizes)
+    int n_chunks = (len + GR_CHUNK - 1) / GR_CHUNK;
+    for (int c = 0; c < GR_STAGES - 1; ++c) {
+        if (c < n_chunks) stage(c * GR_CHUNK, c);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     bool ones = SCALAR && live && col >= vdim;  // the normaliser's column
-    for (int t0 = 0; t0 < len; t0 += GR_CHUNK, b ^= 1) {
+    for (int c = 0; c < n_chunks; ++c) {
+        int t0 = c * GR_CHUNK, b = c % GR_STAGES;
         int cnt = min(GR_CHUNK, len - t0);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // this chunk has landed for everyone, and everyone is done with the other buffer
-        if (t0 + GR_CHUNK < len) stage(t0 + GR_CHUNK, b ^ 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(GR_STAGES - 2) : "memory");
+        __syncthreads();  // this chunk has landed for everyone, and everyone is done with the buffer filled next
+        if (c + GR_STAGES - 1 < n_chunks) stage((c + GR_STAGES - 1) * GR_CHUNK, (c + GR_STAGES - 1) % GR_STAGES);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
         const float* qs = sm + b * BUF + sub;
         const float* ws = qs + GR_CHUNK * DP;
         const float* as = ws + GR_CHUNK * DP;
@@ -312,9 +320,9 @@ int launch_recurrence(const float* q, int q_ld, const float* a, int a_ld, const 
                       const int* slots, const int* cu_q, float* out, int num_seqs, int heads, int dim, int vdim,
                       int cols, float q_scale, int num_slots, cudaStream_t s) {
     constexpr int COLS = GR_THREADS / TPC;
-    size_t smem = (size_t)2 * GR_CHUNK * ((SCALAR ? 2 : 3) * R * TPC + COLS + 4) * sizeof(float);
+    size_t smem = (size_t)GR_STAGES * GR_CHUNK * ((SCALAR ? 2 : 3) * R * TPC + COLS + 4) * sizeof(float);
     static IePerDevice allowed;
-    cudaError_t e = ie_allow_smem(allowed, gated_recurrence_kernel<R, TPC, SCALAR>, 160 * 1024);
+    cudaError_t e = ie_allow_smem(allowed, gated_recurrence_kernel<R, TPC, SCALAR>, 200 * 1024);  // (dim 512: 198 KB)
     if (e != cudaSuccess) return (int)e;
     dim3 grid((cols + COLS - 1) / COLS, heads, num_seqs);
     return ie_launch(gated_recurrence_kernel<R, TPC, SCALAR>, grid, dim3(GR_THREADS), smem, s, q, q_ld, a, a_ld, w,
@@ -382,8 +390,8 @@ IE_API int ie_gated_recurrence(const float* q, int q_ld, const float* a, int a_l
     if (dim <= 16) return launch_recurrence<8, 2, SC>(IE_GR_ARGS);            \
     if (dim <= 32) return launch_recurrence<8, 4, SC>(IE_GR_ARGS);            \
     if (dim <= 64) return launch_recurrence<8, 8, SC>(IE_GR_ARGS);            \
-    if (dim <= 128) return launch_recurrence<16, 8, SC>(IE_GR_ARGS);          \
-    if (dim <= 256) return launch_recurrence<16, 16, SC>(IE_GR_ARGS);         \
+    if (dim <= 128) return launch_recurrence<8, 16, SC>(IE_GR_ARGS);          \
+    if (dim <= 256) return launch_recurrence<8, 32, SC>(IE_GR_ARGS);          \
     if (dim <= 512) return launch_recurrence<16, 32, SC>(IE_GR_ARGS);
     if (gates != nullptr) { IE_GR_PICK(true) } else { IE_GR_PICK(false) }
 #undef IE_GR_PICK

@@ -1,5 +1,5 @@
-// Attention with sigmoid weights and a chunked mask on the tensor cores (bfloat16), for steps that
-// hold portions of prompts.  Built per (key size SA_D, value size SA_DV), both multiples of 16.
+// Attention with sigmoid weights and a chunked mask on the tensor cores (bfloat16), for prompt
+// portions and single tokens alike.  Built per (key size SA_D, value size SA_DV), both multiples of 16.
 //
 // o_i = sum over visible j of sigmoid(q_i . k_j * scale + bias[head]) v_j: no maximum, no sum of
 // weights, nothing to rescale, so a block just adds P V over its key tiles.  A block owns 64
@@ -23,6 +23,7 @@
 namespace {
 constexpr int D = SA_D, DV = SA_DV;
 constexpr int ROWS = 64, KEYS = 64, WARPS = 4, THREADS = WARPS * 32;
+static_assert(THREADS == 2 * KEYS, "two threads bring a key's rows");
 constexpr int LDK = D + 8, LDV = DV + 8;  // rows 16 bytes longer: ldmatrix rows fall on different banks
 static_assert(D % 16 == 0 && DV % 16 == 0 && D <= 256 && DV <= 256, "sizes");
 
@@ -64,7 +65,8 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     __nv_bfloat16* vs = ks + 2 * KEYS * LDK;                    // [2][KEYS][LDV]
     ie_pdl_trigger();
     ie_pdl_wait();
-    int seq = blockIdx.z, head = blockIdx.y, tile = blockIdx.x;
+    // (the blocks of a request's last rows see the most keys of a chunk: they start first)
+    int seq = blockIdx.z, head = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
     int q0 = cu_q[seq], q_len = cu_q[seq + 1] - q0;
     int row0 = tile * ROWS;
     if (row0 >= q_len) return;
@@ -77,34 +79,32 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     const int* table = block_tables + (size_t)seq * table_width;
     int page_shift = 31 - __clz(page_size);
 
+    // Two threads bring a key's rows (key and value), the 16-byte pieces dealt alternately: one look
+    // into the block table per thread and tile, then only copies.
     auto load_tile = [&](int t, int buf) {
-        __nv_bfloat16* kd = ks + (size_t)buf * KEYS * LDK;
-        __nv_bfloat16* vd = vs + (size_t)buf * KEYS * LDV;
         constexpr int KC = D / 8, VC = DV / 8;  // 16-byte pieces of a row
-        for (int i = tid; i < KEYS * (KC + VC); i += THREADS) {
-            int key = i / (KC + VC), c = i - key * (KC + VC);
-            int pos = t * KEYS + key;
-            const __nv_bfloat16* src = k_cache;
-            int bytes = 0;
-            long long row = -1;
-            if (pos >= lo_min && pos <= last_pos) {
-                int page = table[pos >> page_shift];
-                if (page < 0 || page >= total_pages) {
-                    if (c == 0) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, q0 + row0);
-                } else {
-                    row = ((long long)page * kv_heads + kvh) * page_size + (pos & (page_size - 1));
-                    bytes = 16;
-                }
-            }
-            // (what is outside the range reads as zero: its weight is zero too, and 0 * 0 adds nothing)
-            if (c < KC) {
-                if (bytes) src = k_cache + row * D + c * 8;
-                cp_async16z(kd + key * LDK + c * 8, src, bytes);
+        int key = tid >> 1, pos = t * KEYS + key;
+        __nv_bfloat16* kd = ks + ((size_t)buf * KEYS + key) * LDK;
+        __nv_bfloat16* vd = vs + ((size_t)buf * KEYS + key) * LDV;
+        const __nv_bfloat16* ksrc = k_cache;
+        const __nv_bfloat16* vsrc = v_cache;
+        int bytes = 0;
+        if (pos >= lo_min && pos <= last_pos) {
+            int page = table[pos >> page_shift];
+            if (page < 0 || page >= total_pages) {
+                if ((tid & 1) == 0) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, q0 + row0);
             } else {
-                if (bytes) src = v_cache + row * DV + (c - KC) * 8;
-                cp_async16z(vd + key * LDV + (c - KC) * 8, src, bytes);
+                long long row = ((long long)page * kv_heads + kvh) * page_size + (pos & (page_size - 1));
+                ksrc = k_cache + row * D;
+                vsrc = v_cache + row * DV;
+                bytes = 16;
             }
         }
+        // (what is outside the range reads as zero: its weight is zero too, and 0 * 0 adds nothing)
+#pragma unroll
+        for (int c = (tid & 1); c < KC; c += 2) cp_async16z(kd + c * 8, bytes ? ksrc + c * 8 : k_cache, bytes);
+#pragma unroll
+        for (int c = (tid & 1); c < VC; c += 2) cp_async16z(vd + c * 8, bytes ? vsrc + c * 8 : v_cache, bytes);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     int t_begin = lo_min / KEYS, t_end = last_pos / KEYS;  // inclusive
@@ -163,6 +163,8 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                 int key_pos = kp + (e & 1);
                 int pos = e < 2 ? pos_a : pos_b, lo = e < 2 ? lo_a : lo_b;
                 bool visible = key_pos <= pos && key_pos >= lo;
+                // (exponential and reciprocal of the special-function unit: a few units in the last place,
+                // relative also for the small weights far down the sigmoid's tail, which a tanh form loses)
                 w[e] = visible ? __fdividef(1.0f, 1.0f + __expf(-fmaf(s[nt][e], scale, hb))) : 0.f;
             }
             pf[nt >> 1][(nt & 1) * 2] = pack_bf16(w[0], w[1]);

@@ -1203,8 +1203,6 @@ class CudaOps:
             heads, kv_heads, dim, vdim, page_size, k_cache.shape[0], self._err_ptr, self._stream()),
             "qk_norm_rope_write")
 
-    SIGMOID_MMA_MIN_PORTION = 32  # a step whose longest portion has this many tokens runs the tensor-core kernel
-
     def _sigmoid_attention_lib(self, hd: int, vdim: int):
         lib = self._sigattn_libs.get((hd, vdim))
         if lib is None:
@@ -1224,19 +1222,20 @@ class CudaOps:
                           chunk, head_bias, out) -> None:
         """Attention without a softmax: the weight of a visible key is ``sigmoid(score + head_bias[h])``;
         a query sees the keys at or before it in its own chunk of ``chunk`` positions (0: all).
-        bfloat16 steps with a prompt portion of some length run the tensor-core kernel (key and value
-        sizes multiples of 16 up to 256, launched for the step's own lengths, so not in a captured
-        step); single tokens, 32-bit and other sizes the general kernel, whose order of operations
-        does not depend on the batch."""
+        bfloat16 with key and value sizes that are multiples of 16 up to 256 runs the tensor-core
+        kernel (a block per 64 positions of a request and head; lengths and tables are read on the
+        device, and a captured step is launched for the most tokens a request can bring within its
+        bounds); 32-bit and other sizes the general kernel.  Neither kernel's order of operations
+        depends on the batch."""
         if (self.sigmoid_mma and q.dtype == self.torch.bfloat16 and hd % 16 == 0 and vdim % 16 == 0
-                and 16 <= hd <= 256 and 16 <= vdim <= 256 and page_size & (page_size - 1) == 0
-                and getattr(ctx, "bounds", None) is None and not getattr(ctx, "padded", False)
-                and getattr(ctx, "max_q_len", 0) >= self.SIGMOID_MMA_MIN_PORTION):
+                and 16 <= hd <= 256 and 16 <= vdim <= 256 and page_size & (page_size - 1) == 0):
             lib = self._sigmoid_attention_lib(hd, vdim)
+            bounds = getattr(ctx, "bounds", None)
+            longest = bounds[0] if bounds is not None else ctx.max_q_len  # (a captured step: its token bound)
             self._check(lib.ie_sigmoid_attention_mma(
                 q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                 block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(), ctx.num_seqs,
-                ctx.max_q_len, nh, nkv, page_size, k_cache.shape[0], scale, int(chunk or 0), head_bias.data_ptr(),
+                longest, nh, nkv, page_size, k_cache.shape[0], scale, int(chunk or 0), head_bias.data_ptr(),
                 self._err_ptr, self._stream()), "sigmoid_attention_mma")
             return
         self._check(self._paged_attention_generic(
