@@ -189,7 +189,14 @@ gated_recurrence_kernel(const float* __restrict__ q, int q_ld, const float* __re
         int r = sub + TPC * i;
         s[i] = (live && r < dim) ? S[r] : 0.f;
     }
-    for (int i = tid; i < GR_STAGES * BUF; i += GR_THREADS) sm[i] = 0.f;  // entries beyond dim read as zero
+    // entries beyond dim (the copies never touch them) read as zero
+    if (DP > dim) {
+        int pad = DP - dim;
+        for (int i = tid; i < GR_STAGES * GR_CHUNK * ROWS * pad; i += GR_THREADS) {
+            int row = i / pad, c = dim + (i - row * pad);
+            sm[(row / (GR_CHUNK * ROWS)) * BUF + (row % (GR_CHUNK * ROWS)) * DP + c] = 0.f;
+        }
+    }
     __syncthreads();
     int c0 = blockIdx.x * COLS;
     bool vec = (dim % 4 == 0) && (q_ld % 4 == 0) && (w_ld % 4 == 0) && (SCALAR || a_ld % 4 == 0) &&
@@ -248,22 +255,36 @@ gated_recurrence_kernel(const float* __restrict__ q, int q_ld, const float* __re
         const float* as = ws + GR_CHUNK * DP;
         const float* vs = sm + b * BUF + ROWS * GR_CHUNK * DP + my_col;
         const float* gs = sm + b * BUF + ROWS * GR_CHUNK * DP + GR_CHUNK * COLS;
-        for (int tt = 0; tt < cnt; ++tt) {
-            float u = ones ? 1.0f : (live ? vs[tt * COLS] : 0.f);
-            float a_s = 1.0f;
-            if (SCALAR) { a_s = gs[2 * tt]; u *= gs[2 * tt + 1]; }
-            float r4[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: shorter chains, a fixed order
+        // The chunk's tokens in order; their read-outs are summed over a column's lanes together at the
+        // end, so that the exchanges of eight tokens overlap instead of each stalling the next token.
+        float rds[GR_CHUNK];
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                int at = tt * DP + TPC * i;
-                float av = SCALAR ? a_s : as[at];
-                s[i] = fmaf(ws[at], u, s[i] * av);
-                r4[i & 3] = fmaf(s[i], qs[at], r4[i & 3]);
+        for (int tt = 0; tt < GR_CHUNK; ++tt) {
+            rds[tt] = 0.f;
+            if (tt < cnt) {
+                float u = ones ? 1.0f : (live ? vs[tt * COLS] : 0.f);
+                float a_s = 1.0f;
+                if (SCALAR) { a_s = gs[2 * tt]; u *= gs[2 * tt + 1]; }
+                float r4[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums: shorter chains, a fixed order
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    int at = tt * DP + TPC * i;
+                    float av = SCALAR ? a_s : as[at];
+                    s[i] = fmaf(ws[at], u, s[i] * av);
+                    r4[i & 3] = fmaf(s[i], qs[at], r4[i & 3]);
+                }
+                rds[tt] = (r4[0] + r4[1]) + (r4[2] + r4[3]);
             }
-            float rd = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+        }
 #pragma unroll
-            for (int o = TPC >> 1; o > 0; o >>= 1) rd += __shfl_xor_sync(0xffffffffu, rd, o);
-            if (live && sub == 0) out[((size_t)(start + t0 + tt) * heads + head) * cols + col] = rd * q_scale;
+        for (int o = TPC >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int tt = 0; tt < GR_CHUNK; ++tt) rds[tt] += __shfl_xor_sync(0xffffffffu, rds[tt], o);
+        }
+        if (live && sub == 0) {
+#pragma unroll
+            for (int tt = 0; tt < GR_CHUNK; ++tt)
+                if (tt < cnt) out[((size_t)(start + t0 + tt) * heads + head) * cols + col] = rds[tt] * q_scale;
         }
     }
     if (live) {

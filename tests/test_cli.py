@@ -55,3 +55,36 @@ def test_info_prints_a_rugedra_shape(tmp_path, capsys):
     assert "architecture        Rugedra" in out and "layers / width      4 / 72" in out
     assert "channel_delta+moe, latent_attention, latent_attention+dense, channel_delta+dense" in out
     assert "state per request" in out
+
+
+def test_info_prints_a_ravapel_shape(tmp_path, capsys):
+    from tests import ravapel_configs as R
+
+    (tmp_path / "config.json").write_text(json.dumps(R.MIXED))
+    assert cli.main(["info", "--model", str(tmp_path), "--gpu-mem", "180"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture        Ravapel" in out and "layers / width      5 / 72" in out
+    assert "hgrn2+dense, parallel, hgrn2+dense, parallel+dense, hgrn2+dense" in out
+    assert "loop                layers 1..2 x 3" in out and "state per request" in out
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_ravapel_folder(tmp_path, capsys):
+    """`engine generate` on a Ravapel folder: the same entry point, scheduler and sampling as for the
+    other architectures; greedy tokens are the plain implementation's."""
+    import torch
+
+    from tests import plain_ravapel as P
+    from tests import ravapel_configs as R
+
+    cfg, weights = R.ODD, R.make_weights(R.ODD, seed=2)
+    folder = H.write_model_dir(tmp_path / "m", cfg, weights)
+    prompt = [5, 17, 3, 44, 9, 21, 30]
+    rc = cli.main(["generate", "--model", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--temperature", "0",
+                   "--max-tokens", "6", "--dtype", "float32", "--num-blocks", "16", "--block-size", "8",
+                   "--max-num-seqs", "2", "--max-num-batched-tokens", "4"])
+    assert rc == 0
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(P.forward(cfg, weights, ids, torch.float64)[-1].argmax()))
+    assert capsys.readouterr().out.split() == [str(t) for t in ids[len(prompt):]]
