@@ -532,7 +532,7 @@ def ravapel_rows(size: str, kinds: dict, peaks: dict, tokens: int, batch: int, c
         "linear:hgrn2.in": width * hg[0] * (2 * hg[1] + hg[2]), "linear:hgrn2.delta": width * hg[0] * hg[2],
         "linear:sigattn.qkv": width * ((H + G) * d + G * dv), "linear:sigattn.delta": width * H * dv,
         "linear:mlstm.in": width * mm[0] * (2 * mm[1] + 2 * mm[2] + 2), "linear:mlstm.delta": width * mm[0] * mm[2],
-        "linear:ffn.gate_up32": 2 * width * ff, "linear:ffn.delta": width * ff,
+        "linear:ffn.gate_up": 2 * width * ff, "linear:ffn.delta": width * ff,
         "linear:stream.reinject": 2 * width * width, "linear:head": width * DESIGN_VOCAB,
     }
     # the two recurrences share a kind; two layers of each: state floats read and written per request

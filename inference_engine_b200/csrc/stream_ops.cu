@@ -8,7 +8,8 @@
 //  * sandwich_norm: y = sum of the parts of `delta` (+ bias); y <- rms(y) * post_w (if post_w);
 //    h += y; out = rms(h) * pre_w (if out).  One block per row; both sums of squares are added in
 //    an order that depends on the row's width alone.
-//  * silu_mul_bias: out = silu(g + bg) * (u + bu) from 32-bit rows that hold gates, then ups.
+//  * silu_mul_bias: out = silu(g + bg) * (u + bu) from rows that hold gates, then ups (32-bit, or the
+//    compute dtype); biases and activation in 32-bit.
 //  * concat_cast: out[n] = [h[n]; x0[n]] in the compute dtype.
 //  * weighted_sum: out = sa * a + sb * b (32-bit).
 #include "common.cuh"
@@ -166,8 +167,8 @@ sandwich_norm_kernel(float* __restrict__ h, const float* __restrict__ delta, int
     }
 }
 
-template <typename T>
-__global__ void silu_mul_bias_kernel(const float* __restrict__ gate_up, const float* __restrict__ bias,
+template <typename T, typename InT>
+__global__ void silu_mul_bias_kernel(const InT* __restrict__ gate_up, const float* __restrict__ bias,
                                      T* __restrict__ out, int inter, size_t total) {
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -176,7 +177,7 @@ __global__ void silu_mul_bias_kernel(const float* __restrict__ gate_up, const fl
     for (; idx < total; idx += stride) {
         size_t row = idx / inter;
         int i = (int)(idx - row * inter);
-        float g = gate_up[row * 2 * inter + i], u = gate_up[row * 2 * inter + inter + i];
+        float g = ie_load(gate_up + row * 2 * inter + i), u = ie_load(gate_up + row * 2 * inter + inter + i);
         if (bias) { g += bias[i]; u += bias[inter + i]; }
         ie_store(out + idx, g / (1.0f + expf(-g)) * u);
     }
@@ -265,16 +266,21 @@ IE_API int ie_sandwich_norm(float* h, const float* delta, int num_partials, long
 #undef IE_SN_LAUNCH
 }
 
-IE_API int ie_silu_mul_bias(const float* gate_up, const float* bias, void* out, int out_dtype, int num_rows,
-                            int inter, void* stream) {
+// `gate_up` is 32-bit, or has the output's dtype (the product's sums rounded once before the biases).
+IE_API int ie_silu_mul_bias(const void* gate_up, int in_dtype, const float* bias, void* out, int out_dtype,
+                            int num_rows, int inter, void* stream) {
     size_t total = (size_t)num_rows * inter;
     if (total == 0) return 0;
+    if (in_dtype != IE_F32 && in_dtype != out_dtype) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16 && in_dtype == IE_BF16)
+        return ie_launch(silu_mul_bias_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0,
+                         s, (const __nv_bfloat16*)gate_up, bias, (__nv_bfloat16*)out, inter, total);
     if (out_dtype == IE_BF16)
-        return ie_launch(silu_mul_bias_kernel<__nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0, s, gate_up,
-                         bias, (__nv_bfloat16*)out, inter, total);
-    return ie_launch(silu_mul_bias_kernel<float>, dim3(grid_for(total, 256)), dim3(256), 0, s, gate_up, bias,
-                     (float*)out, inter, total);
+        return ie_launch(silu_mul_bias_kernel<__nv_bfloat16, float>, dim3(grid_for(total, 256)), dim3(256), 0, s,
+                         (const float*)gate_up, bias, (__nv_bfloat16*)out, inter, total);
+    return ie_launch(silu_mul_bias_kernel<float, float>, dim3(grid_for(total, 256)), dim3(256), 0, s,
+                     (const float*)gate_up, bias, (float*)out, inter, total);
 }
 
 IE_API int ie_concat_cast(const float* a, const float* b, void* out, int out_dtype, int num_rows, int width,

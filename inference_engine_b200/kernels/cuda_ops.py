@@ -217,7 +217,7 @@ class CudaOps:
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
             "ie_bigram_embedding": [P, P, I, P, P, P, P, P, P, L, I, P, I, I, I, I, L, L, P, P],
             "ie_sandwich_norm": [P, P, I, L, P, P, F, P, F, P, I, P, I, I, P],
-            "ie_silu_mul_bias": [P, P, P, I, I, I, P],
+            "ie_silu_mul_bias": [P, I, P, P, I, I, I, P],
             "ie_concat_cast": [P, P, P, I, I, I, P],
             "ie_weighted_sum": [P, F, P, F, P, L, P],
         }
@@ -1106,11 +1106,12 @@ class CudaOps:
 
     @_kind("activation")
     def silu_mul_bias(self, gate_up, bias, out) -> None:
-        """``out = silu(g + bias_g) * (u + bias_u)`` from 32-bit rows of gates, then ups."""
-        if gate_up.dtype != self.torch.float32 or gate_up.shape[1] != 2 * out.shape[1]:
-            raise KernelError("silu_mul_bias reads 32-bit rows of gates and ups")
-        self._check(self._silu_mul_bias(gate_up.data_ptr(), self._ptr(bias), out.data_ptr(), _dtype_code(out),
-                                        out.shape[0], out.shape[1], self._stream()), "silu_mul_bias")
+        """``out = silu(g + bias_g) * (u + bias_u)`` from rows of gates, then ups (32-bit or ``out``'s
+        dtype); biases and activation in 32-bit."""
+        if gate_up.dtype not in (self.torch.float32, out.dtype) or gate_up.shape[1] != 2 * out.shape[1]:
+            raise KernelError("silu_mul_bias reads rows of gates and ups, 32-bit or of the output's dtype")
+        self._check(self._silu_mul_bias(gate_up.data_ptr(), _dtype_code(gate_up), self._ptr(bias), out.data_ptr(),
+                                        _dtype_code(out), out.shape[0], out.shape[1], self._stream()), "silu_mul_bias")
 
     @_kind("stream")
     def concat_cast(self, a, b, out) -> None:

@@ -6,7 +6,7 @@ unchanged, and a kernel that owns a tile of rows then holds each gate beside its
 apply the activation itself (``ops.gated_linear``).
 
 With biases (``gate_bias``, ``up_bias``, ``down_bias``: tensor names) gate and up are stacked in
-halves, their product comes back in 32-bit and biases and activation are one kernel; the down
+halves, their product comes back in the compute dtype and biases (added in 32-bit) and activation are one kernel; the down
 projection's bias is not added here: the block's norm after the feed-forward takes it
 (``output_bias``), so only a block with such a norm can hold a feed-forward with a down bias."""
 
@@ -78,7 +78,7 @@ class SwiGLU(FeedForward):
         import torch
 
         if self.bias_gate_up is not None:
-            gate_up = ctx.ops.linear(x, self.w_gate_up, ws=ctx.ws, tag="ffn.gate_up32", out_dtype=torch.float32)
+            gate_up = ctx.ops.linear(x, self.w_gate_up, ws=ctx.ws, tag="ffn.gate_up", out_dtype=self.dtype)
             act = ctx.ws.buffer("ffn.act", x.shape[0], self.intermediate_size, self.dtype)
             ctx.ops.silu_mul_bias(gate_up, self.bias_gate_up, act)
         else:

@@ -30,7 +30,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--config", default=None, help="a config.json file (default: Llama 3.2 1B shape)")
+    ap.add_argument("--config", default=None,
+                    help="a config.json file of any registered architecture (default: Llama 3.2 1B shape)")
     ap.add_argument("--graphs", action="store_true", help="replay captured decode steps")
     ap.add_argument("--phase-clocks", action="store_true",
                     help="prefill: clocks per key tile in each phase of a softmax thread of the tcgen05 attention")
@@ -57,7 +58,8 @@ def main() -> int:
                              "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
             "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
         }
-    cfg["num_hidden_layers"] = args.layers
+    if "num_hidden_layers" in cfg:  # (a design that lists its layers one by one keeps its own)
+        cfg["num_hidden_layers"] = args.layers
     block = 16
     per_req = {"decode": args.context, "prefill": args.tokens,
                "mixed": max(args.context, args.prompt_tokens)}[args.mode] + args.steps + args.warmup + 16
@@ -66,7 +68,7 @@ def main() -> int:
         num_blocks=args.batch * (-(-per_req // block) + 1), block_size=block,
         max_num_seqs=args.batch, max_num_batched_tokens=max(args.tokens, args.batch, 2048),
         enable_cuda_graphs=args.graphs)
-    runner, cache, vocab = engine.runner, engine.cache, cfg["vocab_size"]
+    runner, cache, vocab = engine.runner, engine.cache, cfg.get("vocab_size", cfg.get("vocab"))
     g = torch.Generator().manual_seed(0)
     times = []
     if args.mode == "prefill":
