@@ -183,6 +183,39 @@ __global__ void silu_mul_bias_kernel(const InT* __restrict__ gate_up, const floa
     }
 }
 
+// bfloat16 in and out, width a multiple of 8: a thread takes eight gates and their ups as two 16-byte
+// loads, the row from the grid (no division); biases, activation in 32-bit (precise exponential and divide).
+__global__ void __launch_bounds__(256)
+silu_mul_bias_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, const float* __restrict__ bias,
+                            __nv_bfloat16* __restrict__ out, int inter) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    size_t row = blockIdx.y;
+    int v = blockIdx.x * 256 + threadIdx.x;
+    if (v >= inter / 8) return;
+    const __nv_bfloat16* g_row = gate_up + row * 2 * inter;
+    uint4 graw = *reinterpret_cast<const uint4*>(g_row + v * 8);
+    uint4 uraw = *reinterpret_cast<const uint4*>(g_row + inter + v * 8);
+    float bg[8], bu[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        bg[j] = bias ? bias[v * 8 + j] : 0.f;
+        bu[j] = bias ? bias[inter + v * 8 + j] : 0.f;
+    }
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 oraw;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+        float g0 = gf.x + bg[2 * j], g1 = gf.y + bg[2 * j + 1];
+        float u0 = uf.x + bu[2 * j], u1 = uf.y + bu[2 * j + 1];
+        o2[j] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+    }
+    *reinterpret_cast<uint4*>(out + row * inter + (size_t)v * 8) = oraw;
+}
+
 template <typename T>
 __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
                                    int width, size_t total) {
@@ -273,6 +306,9 @@ IE_API int ie_silu_mul_bias(const void* gate_up, int in_dtype, const float* bias
     if (total == 0) return 0;
     if (in_dtype != IE_F32 && in_dtype != out_dtype) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == IE_BF16 && in_dtype == IE_BF16 && inter % 8 == 0 && num_rows <= 65535)
+        return ie_launch(silu_mul_bias_bf16x8_kernel, dim3((unsigned)((inter / 8 + 255) / 256), (unsigned)num_rows),
+                         dim3(256), 0, s, (const __nv_bfloat16*)gate_up, bias, (__nv_bfloat16*)out, inter);
     if (out_dtype == IE_BF16 && in_dtype == IE_BF16)
         return ie_launch(silu_mul_bias_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid_for(total, 256)), dim3(256), 0,
                          s, (const __nv_bfloat16*)gate_up, bias, (__nv_bfloat16*)out, inter, total);

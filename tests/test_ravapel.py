@@ -462,6 +462,26 @@ def test_norm_add_norm_in_one_kernel(device, hidden):
     assert torch.equal(hd2.cpu(), h)
 
 
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("inter", [24, 30, 1096])
+def test_gated_activation_with_biases(device, inter):
+    ops, g = _ops(device), torch.Generator().manual_seed(inter)
+    n = 5
+    gate_up, bias = torch.randn(n, 2 * inter, generator=g) * 3, torch.randn(2 * inter, generator=g)
+    want = torch.nn.functional.silu(gate_up[:, :inter].double() + bias[:inter].double()) * (
+        gate_up[:, inter:].double() + bias[inter:].double())
+    out = torch.zeros(n, inter, device=device)
+    ops.silu_mul_bias(gate_up.to(device), bias.to(device), out)
+    torch.testing.assert_close(out.cpu(), want.float(), atol=1e-5, rtol=1e-5)
+    # the product rounded to bfloat16 first (what the bfloat16 path hands over), biases added in 32-bit
+    rounded = gate_up.to(torch.bfloat16)
+    want16 = torch.nn.functional.silu(rounded[:, :inter].double() + bias[:inter].double()) * (
+        rounded[:, inter:].double() + bias[inter:].double())
+    out16 = torch.zeros(n, inter, device=device, dtype=torch.bfloat16)
+    ops.silu_mul_bias(rounded.to(device), bias.to(device), out16)
+    torch.testing.assert_close(out16.float().cpu(), want16.float(), atol=1e-2, rtol=1e-2)
+
+
 # --- long decoding and generation through the engine ------------------------------------------------
 
 
