@@ -536,3 +536,45 @@ def test_greedy_generation_through_the_engine(name):
         assert got[rid] == _greedy_plain(cfg, weights, prompt, 10), rid
     engine.cache.check_invariants()
     assert engine.cache.slots.num_free == engine.cache.slots.num_slots
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_short_steps_with_portions(tmp_path, dtype):
+    """Portions and mixed batches replayed through captured launch sequences (launched for bounds, padded
+    with tokens that belong to no request): key and value sizes the tensor-core attention takes, so in
+    bfloat16 that kernel runs sized by the token bound.  Against the plain implementation; in 32-bit
+    equal bit for bit to the eagerly launched steps."""
+    from inference_engine_b200.engine.graphs import DecodeGraphs, MixedGraphs
+    from inference_engine_b200.kernels import get_ops
+
+    cfg = R.config(64, 89, [
+        (R.hgrn2(2, 16, 24), R.dense(48)),
+        (R.parallel(R.left(4, 2, 16, 32, chunk=24, rot_dims=8), R.right(2, 8, 16)), R.dense(64)),
+        (R.parallel(R.left(2, 1, 32, 16, chunk=9), R.right(3, 4, 8)), None),
+    ], taps=2, loop=(1, 3, 2))
+    weights = R.make_weights(cfg, seed=6)
+    requests = _requests(cfg, [70, 45, 33, 90, 20, 60], seed=300)
+    want = _want(cfg, weights, requests)
+    tol = (_float32_bound(cfg, weights, requests, want) if dtype == "float32"
+           else _bfloat16_bound(tmp_path, cfg, weights, requests, want))
+    mixed, peak = H.trace_mixed(requests, seed=2, tail=6, max_portion=20)
+    results = {}
+    for captured in (True, False):
+        for mode, (trace, room) in {"portions": (H.trace_portions(requests), 128), "mixed": (mixed, peak)}.items():
+            session = _session(tmp_path / f"{mode}{captured}", cfg, weights, dtype, "cuda", get_ops("cuda"), room, 8)
+            if captured:
+                graphs = MixedGraphs(DecodeGraphs(session.runner, 256, max(64, -(-room // 8))))
+                eager = session.runner.step
+                session.runner.step = lambda entries, g=graphs, e=eager: g.run(entries) if g.can_run(entries) else e(entries)
+            got = H.collect(session, trace)
+            for rid in requests:
+                H.assert_close(got[rid], want[rid], dtype, f"captured={captured} {mode} {rid}", tol)
+            if captured:
+                assert graphs.replays > len(requests)
+            results[(captured, mode)] = got
+    if dtype == "float32":
+        for mode in ("portions", "mixed"):
+            for rid in requests:
+                assert torch.equal(results[(True, mode)][rid], results[(False, mode)][rid]), (mode, rid)
+    get_ops("cuda").check_errors()
