@@ -140,6 +140,16 @@ def test_layout_of_the_model_and_its_caches():
     assert [(g.chunk, g.value_dim) for g in plain.paged_groups] == [(None, 8)]
 
 
+@pytest.mark.parametrize("name", list(R.CONFIGS))
+def test_footprint_formula_counts_what_the_model_declares(name):
+    from inference_engine_b200.architectures.ravapel import ravapel_footprint
+    from inference_engine_b200.config import build_model_spec, config_from_dict
+    from inference_engine_b200.engine.model import Model
+
+    cfg = config_from_dict(R.CONFIGS[name])
+    assert ravapel_footprint(cfg) == Model(build_model_spec(cfg), "float32", 64).footprint()
+
+
 def test_configuration_errors():
     from inference_engine_b200.config import ConfigError, config_from_dict
 
