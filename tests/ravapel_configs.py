@@ -72,6 +72,15 @@ RECURRENT = config(48, 61, [
     (hgrn2(2, 24, 6), None),
 ], taps=None, loop=(1, 2, 2))
 
+# larger than the others: key and value sizes that the tensor-core attention takes (48 and 80, 96 and 96),
+# key sizes of the recurrences with more than one row group per lane, chunks of 100 and 64 positions
+# (longer than, and as long as, a key tile), a loop over the first two layers
+WIDE = config(160, 301, [
+    (parallel(left(6, 3, 48, 80, chunk=100, rot_dims=24), right(4, 24, 40)), dense(256)),
+    (hgrn2(5, 40, 56), dense(200)),
+    (parallel(left(8, 2, 96, 96, chunk=64, rot_dims=96, base=300.0), right(2, 72, 24), 0.5, 0.9), dense(128)),
+], taps=4, bigram=(211, 31, 7), loop=(0, 2, 2), max_positions=512)
+
 CONFIGS = {"mixed": MIXED, "plain": PLAIN, "odd": ODD, "recurrent": RECURRENT}
 
 

@@ -116,6 +116,43 @@ def test_every_way_of_cutting_on_the_gpu(tmp_path, name, dtype):
     get_ops("cuda").check_errors()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_long_prompts(tmp_path, dtype):
+    """Prompts of hundreds of tokens over several chunks and many pages of 16, sizes that reach the
+    tensor-core attention in bfloat16 and the wider instances of the recurrence."""
+    from inference_engine_b200.kernels import get_ops
+
+    cfg = R.WIDE
+    weights = R.make_weights(cfg, seed=21)
+    requests = _requests(cfg, [420, 130, 257, 64], seed=900)
+    want = _want(cfg, weights, requests)
+    tol = (_float32_bound(cfg, weights, requests, want) if dtype == "float32"
+           else _bfloat16_bound(tmp_path, cfg, weights, requests, want))
+    mixed, peak = H.trace_mixed(requests, seed=8, tail=20, max_portion=90)
+    room = sum(H.round64(len(t)) for t in requests.values())
+    before = dict(get_ops("cuda").launch_counts)
+    results = {}
+    for mode, (trace, space) in {"whole": (H.trace_whole(requests), room),
+                                 "tail": (H.trace_decode_tail(requests, 40), room),
+                                 "portions": (H.trace_portions(requests, (70, 2, 129, 3, 64, 33)), room),
+                                 "mixed": (mixed, peak)}.items():
+        session = _session(tmp_path / mode, cfg, weights, dtype, "cuda", get_ops("cuda"), space, 16)
+        results[mode] = H.collect(session, trace)
+        for rid in requests:
+            H.assert_close(results[mode][rid], want[rid], dtype, f"wide {mode} {rid}", tol)
+        assert session.cache.num_free_pages == [p.num_pages for p in session.cache.pools]
+    ran = get_ops("cuda").launch_counts.get("sigmoid_attention_mma", 0) - before.get("sigmoid_attention_mma", 0)
+    if dtype == "float32":
+        assert ran == 0
+        for mode in ("tail", "portions", "mixed"):
+            for rid in requests:
+                assert torch.equal(results["whole"][rid], results[mode][rid]), (mode, rid)
+    else:
+        assert ran > 0  # (the tensor-core kernel did serve these sizes)
+    get_ops("cuda").check_errors()
+
+
 def test_layout_of_the_model_and_its_caches():
     from inference_engine_b200.config import build_model_spec, config_from_dict
     from inference_engine_b200.engine.model import Model
