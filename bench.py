@@ -515,8 +515,8 @@ def ravapel_config(size: str) -> dict:
     dense = {"kind": "dense", "ff": ff}
     layers = [("hgrn2", hgrn2), ("parallel", parallel), ("parallel", parallel), ("hgrn2", hgrn2)]
     return {"architecture": "Ravapel", "vocab": DESIGN_VOCAB, "width": width, "max_positions": MAX_CONTEXT,
-            "norm": {"eps": 1e-6}, "canon": {"taps": taps},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 17}},
+            "norm": {"eps": 1e-5}, "canon": {"taps": taps},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}},
             "loop": {"start": 1, "stop": 3, "times": 1},
             "layers": [{"type": t, "mixer": m, "mlp": dense} for t, m in layers]}
 

@@ -350,7 +350,7 @@ def _paged(x, page_size, pages_total, order, device):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("chunk", [None, 1, 5, 12, 200])
+@pytest.mark.parametrize("chunk", [None, 1, 5, 12, 150])
 def test_sigmoid_attention_sees_exactly_its_chunk(device, chunk):
     """One key per query stands out (score +30 against a bias of -15, every other score near -15,
     so weights of 1 and of 1e-7): the key just inside the query's chunk, or the one just before the
@@ -389,7 +389,7 @@ def test_sigmoid_attention_sees_exactly_its_chunk(device, chunk):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("d,dv,chunk", [(16, 32, 50), (64, 64, None), (128, 128, 200), (48, 16, 64), (128, 64, 1)])
+@pytest.mark.parametrize("d,dv,chunk", [(16, 32, 50), (64, 64, None), (128, 128, 160), (48, 16, 64), (128, 64, 1)])
 def test_sigmoid_attention_on_the_tensor_cores(d, dv, chunk):
     """The bfloat16 kernel for prompt portions against the plain function: portions that start and end
     inside chunks and tiles, two requests of unequal length in one step (one of them a single token),
