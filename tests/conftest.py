@@ -30,7 +30,7 @@ def pytest_terminal_summary(terminalreporter):
     from tests import helpers
 
     for dtype, seen in sorted(helpers.ACHIEVED.items()):
-        bounds = helpers.TOL[dtype]
+        bounds = helpers.TOL.get(dtype, "measured per configuration: three times what rounding alone does")
         terminalreporter.write_line(
             f"logits vs plain implementation, {dtype}: " + ", ".join(
                 f"{k} {v:.3g}" for k, v in sorted(seen.items())) + f"  (bounds: {bounds})")

@@ -19,6 +19,8 @@ from tests import ravapel_configs as R
 
 LENGTHS = [50, 21, 37, 64, 9, 1]
 BF16_TOL = dict(atol=0.35, rtol=0.0, pos_rel_rms=0.08, rel_rms=0.04)
+# (under these names the run's summary lists this file's comparisons: their bounds are measured)
+LABEL = {"float32": "float32, Ravapel", "bfloat16": "bfloat16, Ravapel"}
 
 
 def _requests(cfg, lengths=LENGTHS, seed=700):
@@ -87,7 +89,7 @@ def _run_all_modes(tmp_path, name, dtype, device, ops, page_size=4, lengths=LENG
         session = _session(tmp_path, cfg, weights, dtype, device, ops, room, page_size)
         got = H.collect(session, trace)
         for rid in requests:
-            H.assert_close(got[rid], want[rid], dtype, f"ravapel {name} {mode} {rid}", tol)
+            H.assert_close(got[rid], want[rid], LABEL[dtype], f"ravapel {name} {mode} {rid}", tol)
         # everything went back to the pools
         assert session.cache.num_free_pages == [p.num_pages for p in session.cache.pools]
         assert session.cache.slots.num_free == session.cache.slots.num_slots
@@ -140,7 +142,7 @@ def test_a_wider_model_with_long_prompts(tmp_path, dtype):
         session = _session(tmp_path / mode, cfg, weights, dtype, "cuda", get_ops("cuda"), space, 16)
         results[mode] = H.collect(session, trace)
         for rid in requests:
-            H.assert_close(results[mode][rid], want[rid], dtype, f"wide {mode} {rid}", tol)
+            H.assert_close(results[mode][rid], want[rid], LABEL[dtype], f"wide {mode} {rid}", tol)
         assert session.cache.num_free_pages == [p.num_pages for p in session.cache.pools]
     ran = get_ops("cuda").launch_counts.get("sigmoid_attention_mma", 0) - before.get("sigmoid_attention_mma", 0)
     if dtype == "float32":
@@ -545,7 +547,7 @@ def test_long_decoding_through_state_and_pages(tmp_path, dtype):
     want = P.forward(cfg, weights, toks, torch.float64).float()
     session = _session(tmp_path, cfg, weights, dtype, "cuda", get_ops("cuda"), 448, 16)
     got = H.collect(session, H.trace_decode_tail({"a": toks}, 400))["a"]
-    H.assert_close(got, want, dtype, "long decoding",
+    H.assert_close(got, want, LABEL[dtype], "long decoding",
                    _float32_bound(cfg, weights, {"a": toks}, {"a": want}) if dtype == "float32"
                    else _bfloat16_bound(tmp_path, cfg, weights, {"a": toks}, {"a": want}))
 
@@ -616,7 +618,7 @@ def test_captured_short_steps_with_portions(tmp_path, dtype):
                 session.runner.step = lambda entries, g=graphs, e=eager: g.run(entries) if g.can_run(entries) else e(entries)
             got = H.collect(session, trace)
             for rid in requests:
-                H.assert_close(got[rid], want[rid], dtype, f"captured={captured} {mode} {rid}", tol)
+                H.assert_close(got[rid], want[rid], LABEL[dtype], f"captured={captured} {mode} {rid}", tol)
             if captured:
                 assert graphs.replays > len(requests)
             results[(captured, mode)] = got
