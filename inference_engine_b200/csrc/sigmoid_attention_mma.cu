@@ -7,7 +7,8 @@
 // the 64-key tiles from the chunk of its first row to the position of its last row.  Key and value
 // tiles come from the request's pages by cp.async into two buffers; S = Q K^T and O += P V by
 // mma.sync.m16n8k16 with fragments from ldmatrix (values transposed on the way); scores, weights and
-// the mask are 32-bit, the weights rounded to bfloat16 for the second product; O stays in registers.
+// the mask are 32-bit, and a weight enters the second product as two bfloat16 terms (its rounded value
+// and the remainder), so it keeps 16 bits of mantissa; O stays in registers.
 // A row's result depends on its own request alone (tiles are aligned to position 0, keys are added
 // in rising order).
 #include "common.cuh"
@@ -46,6 +47,7 @@ __device__ __forceinline__ void ldsm_x4_trans(unsigned* r, const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -153,7 +155,9 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
             }
         }
         // weights: sigmoid(score * scale + bias) where the key is visible, zero elsewhere
-        unsigned pf[KEYS / 16][4];
+        // (a weight goes into the second product as two bfloat16 terms, its rounded value and what the
+        // rounding left: 16 bits of mantissa, so that the weights stay 32-bit numbers to within 2^-17)
+        unsigned pf[KEYS / 16][4], pl[KEYS / 16][4];
 #pragma unroll
         for (int nt = 0; nt < KEYS / 8; ++nt) {
             int kp = t * KEYS + nt * 8 + t4 * 2;
@@ -169,6 +173,8 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
             }
             pf[nt >> 1][(nt & 1) * 2] = pack_bf16(w[0], w[1]);
             pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(w[2], w[3]);
+            pl[nt >> 1][(nt & 1) * 2] = pack_bf16(w[0] - bf16_round(w[0]), w[1] - bf16_round(w[1]));
+            pl[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(w[2] - bf16_round(w[2]), w[3] - bf16_round(w[3]));
         }
 #pragma unroll
         for (int kk = 0; kk < KEYS / 16; ++kk) {
@@ -178,6 +184,8 @@ sigmoid_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                 ldsm_x4_trans(b, vt + (kk * 16 + (lane & 15)) * LDV + nt * 8 + (lane >> 4) * 8);
                 mma_bf16(o[nt], pf[kk], b[0], b[1]);
                 mma_bf16(o[nt + 1], pf[kk], b[2], b[3]);
+                mma_bf16(o[nt], pl[kk], b[0], b[1]);
+                mma_bf16(o[nt + 1], pl[kk], b[2], b[3]);
             }
         }
     }
